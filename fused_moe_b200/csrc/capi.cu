@@ -1,0 +1,381 @@
+// C ABI of the library (declared in include/b200moe.h): argument checks, workspace
+// carve-up, TMA descriptors, and the launch sequence of one layer call.
+//
+// Launch sequence of b200moe_run (all on the caller's stream, nothing allocated):
+//   memset counters | route (+histogram) | scan | place | gather | GEMM1(+SwiGLU,+row max)
+//   | requant | GEMM2(+weighted combine) | finalize(bf16)
+// It replaces the two Python pipelines of the reference
+// (solution/python/kernel.py:381-429 and 432-572), which need a host synchronisation
+// above 2048 tokens (kernel.py:196); here tile counts stay on the device.
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "common.cuh"
+#include "kernels.cuh"
+
+using namespace b200moe;
+
+namespace {
+
+thread_local char g_cuda_error[256] = "";
+
+int cuda_fail(cudaError_t e, const char* what) {
+  snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s", what, cudaGetErrorString(e));
+  return B200MOE_ERR_CUDA;
+}
+
+#define CUDA_TRY(expr)                                  \
+  do {                                                  \
+    cudaError_t _e = (expr);                            \
+    if (_e != cudaSuccess) return cuda_fail(_e, #expr); \
+  } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct DeviceInfo {
+  bool ready = false;
+  int num_sms = 0;
+};
+
+std::mutex g_mutex;
+EncodeTiledFn g_encode = nullptr;
+DeviceInfo g_dev[64];
+
+// Once per process: the driver entry point for tensor-map encoding; once per device: the
+// SM count and the opt-in shared memory sizes of the GEMM kernels.
+int ensure_device(int* num_sms) {
+  int dev = 0;
+  CUDA_TRY(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return B200MOE_ERR_INVALID_ARGUMENT;
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (qres != cudaDriverEntryPointSuccess || !fn) {
+      snprintf(g_cuda_error, sizeof(g_cuda_error), "cuTensorMapEncodeTiled not available from this driver");
+      return B200MOE_ERR_CUDA;
+    }
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  if (!g_dev[dev].ready) {
+    cudaDeviceProp prop;
+    CUDA_TRY(cudaGetDeviceProperties(&prop, dev));
+    if (prop.major != 10) {
+      snprintf(g_cuda_error, sizeof(g_cuda_error), "device %d is sm_%d%d; this library is built for sm_100a only",
+               dev, prop.major, prop.minor);
+      return B200MOE_ERR_CUDA;
+    }
+    g_dev[dev].num_sms = prop.multiProcessorCount;
+    CUDA_TRY(configure_grouped_gemm());
+    g_dev[dev].ready = true;
+  }
+  *num_sms = g_dev[dev].num_sms;
+  return B200MOE_OK;
+}
+
+// rows x K e4m3 matrix, row pitch `pitch` bytes; box = box_rows x 128 bytes, 128-byte swizzle.
+int make_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64_t k, uint64_t pitch, uint32_t box_rows) {
+  cuuint64_t dims[2] = {k, rows};
+  cuuint64_t strides[1] = {pitch};
+  cuuint32_t box[2] = {(cuuint32_t)kBlockK, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_cuda_error, sizeof(g_cuda_error), "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+    return B200MOE_ERR_CUDA;
+  }
+  return B200MOE_OK;
+}
+
+uint64_t align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
+
+int shape_ok(int T, int e_local, int hidden, int inter) {
+  if (T < 0 || e_local < 1) return B200MOE_ERR_INVALID_ARGUMENT;
+  if (e_local > kNumExperts || hidden < 256 || hidden % 256 != 0 || inter < 128 || inter % 128 != 0)
+    return B200MOE_ERR_UNSUPPORTED_SHAPE;
+  if ((long long)T * kTopK > (1ll << 30)) return B200MOE_ERR_UNSUPPORTED_SHAPE;
+  return B200MOE_OK;
+}
+
+void compute_layout(int T, int e_local, int hidden, int inter, b200moe_ws_layout* L) {
+  memset(L, 0, sizeof(*L));
+  const int n_chunks = T > 0 ? (T + kChunkTokens - 1) / kChunkTokens : 1;
+  const long long pairs = (long long)T * (e_local < kTopK ? e_local : kTopK);
+  const long long m_cap = (long long)align_up((uint64_t)pairs, kTileM) + (long long)kTileM * e_local;
+  L->m_cap = (int32_t)m_cap;
+  L->max_tiles = (int32_t)(m_cap / kTileM);
+  L->n_chunks = n_chunks;
+  L->chunk_tokens = kChunkTokens;
+  uint64_t off = 0;
+  auto take = [&](uint64_t bytes) { uint64_t o = off; off = align_up(off + bytes, 256); return o; };
+  L->status = take(16 * 4);
+  L->meta = take(8 * 4);
+  L->chunk_counts = take((uint64_t)n_chunks * e_local * 4);
+  L->chunk_base = take((uint64_t)n_chunks * e_local * 4);
+  L->expert_count = take((uint64_t)e_local * 4);
+  L->expert_row0 = take((uint64_t)(e_local + 1) * 4);
+  L->tile_expert = take((uint64_t)L->max_tiles * 4);
+  L->row_token = take((uint64_t)m_cap * 4);
+  L->row_weight = take((uint64_t)m_cap * 4);
+  L->a_packed = take((uint64_t)m_cap * hidden);
+  L->a_scale = take((uint64_t)(hidden / kBlockK) * m_cap * 4);
+  L->act = take((uint64_t)m_cap * inter * 4);
+  L->row_amax = take((uint64_t)m_cap * 4);
+  L->act_q = take((uint64_t)m_cap * inter);
+  L->row_scale = take((uint64_t)m_cap * 4);
+  L->out_acc = take((uint64_t)(T > 0 ? T : 1) * hidden * 4);
+  L->topk_ids = take((uint64_t)(T > 0 ? T : 1) * kTopK * 4);
+  L->topk_w = take((uint64_t)(T > 0 ? T : 1) * kTopK * 4);
+  L->total_bytes = off;
+}
+
+int bind_workspace(int T, int e_local, int hidden, int inter, void* workspace, size_t bytes, Workspace* ws) {
+  int rc = shape_ok(T, e_local, hidden, inter);
+  if (rc != B200MOE_OK) return rc;
+  if (!workspace) return B200MOE_ERR_INVALID_ARGUMENT;
+  if (reinterpret_cast<uintptr_t>(workspace) % 256 != 0) return B200MOE_ERR_MISALIGNED;
+  compute_layout(T, e_local, hidden, inter, &ws->L);
+  if (bytes < ws->L.total_bytes) return B200MOE_ERR_WORKSPACE_TOO_SMALL;
+  ws->base = reinterpret_cast<uint8_t*>(workspace);
+  return B200MOE_OK;
+}
+
+// Clears the status word and the histogram (start of a layer call).
+int clear_counters(const Workspace& ws, int e_local, cudaStream_t stream) {
+  // status, meta, chunk_counts are adjacent: one memset covers them
+  size_t bytes = (size_t)(ws.L.chunk_counts - ws.L.status) + (size_t)ws.L.n_chunks * e_local * 4;
+  CUDA_TRY(cudaMemsetAsync(ws.base + ws.L.status, 0, bytes, stream));
+  return B200MOE_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200moe_version(void) { return 1; }
+
+const char* b200moe_status_string(int status) {
+  switch (status) {
+    case B200MOE_OK: return "ok";
+    case B200MOE_ERR_INVALID_ARGUMENT: return "invalid argument";
+    case B200MOE_ERR_UNSUPPORTED_SHAPE: return "unsupported shape";
+    case B200MOE_ERR_WORKSPACE_TOO_SMALL: return "workspace too small";
+    case B200MOE_ERR_CUDA: return "CUDA call failed";
+    case B200MOE_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait timed out";
+    case B200MOE_ERR_MISALIGNED: return "misaligned pointer or stride";
+    default: return "unknown status";
+  }
+}
+
+const char* b200moe_last_cuda_error(void) { return g_cuda_error; }
+
+int b200moe_workspace_layout(int T, int e_local, int hidden, int inter, b200moe_ws_layout* layout) {
+  int rc = shape_ok(T, e_local, hidden, inter);
+  if (rc != B200MOE_OK) return rc;
+  b200moe_ws_layout L;
+  compute_layout(T, e_local, hidden, inter, &L);
+  if (layout) *layout = L;
+  return B200MOE_OK;
+}
+
+int b200moe_launches_per_run(int T, int e_local) {
+  (void)e_local;
+  return T > 0 ? 8 : 0;   // route, scan, place, gather, gemm1, requant, gemm2, finalize
+}
+
+int b200moe_route(const void* logits, int logits_dtype, const void* bias, int bias_dtype, int T,
+                  float routed_scaling_factor, int local_expert_offset, int e_local, int hidden, int inter,
+                  int32_t* topk_ids, float* topk_w, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!logits || !bias || !topk_ids || !topk_w) return B200MOE_ERR_INVALID_ARGUMENT;
+  if ((logits_dtype != B200MOE_F32 && logits_dtype != B200MOE_BF16) ||
+      (bias_dtype != B200MOE_F32 && bias_dtype != B200MOE_BF16))
+    return B200MOE_ERR_INVALID_ARGUMENT;
+  if (local_expert_offset < 0 || local_expert_offset + e_local > kNumExperts) return B200MOE_ERR_INVALID_ARGUMENT;
+  Workspace ws;
+  int rc = bind_workspace(T, e_local, hidden, inter, workspace, workspace_bytes, &ws);
+  if (rc != B200MOE_OK) return rc;
+  int num_sms = 0;
+  if ((rc = ensure_device(&num_sms)) != B200MOE_OK) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if ((rc = clear_counters(ws, e_local, st)) != B200MOE_OK) return rc;
+  CUDA_TRY(launch_route(logits, logits_dtype, bias, bias_dtype, T, routed_scaling_factor, local_expert_offset, e_local,
+                        topk_ids, topk_w, ws.at<int>(ws.L.chunk_counts), num_sms, st));
+  return B200MOE_OK;
+}
+
+int b200moe_count(const int32_t* topk_ids, int64_t ids_row_stride, int T, int local_expert_offset, int e_local,
+                  int hidden, int inter, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!topk_ids || ids_row_stride < kTopK) return B200MOE_ERR_INVALID_ARGUMENT;
+  if (local_expert_offset < 0 || local_expert_offset + e_local > kNumExperts) return B200MOE_ERR_INVALID_ARGUMENT;
+  Workspace ws;
+  int rc = bind_workspace(T, e_local, hidden, inter, workspace, workspace_bytes, &ws);
+  if (rc != B200MOE_OK) return rc;
+  int num_sms = 0;
+  if ((rc = ensure_device(&num_sms)) != B200MOE_OK) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if ((rc = clear_counters(ws, e_local, st)) != B200MOE_OK) return rc;
+  CUDA_TRY(launch_count(topk_ids, ids_row_stride, T, local_expert_offset, e_local, ws.at<int>(ws.L.chunk_counts),
+                        num_sms, st));
+  return B200MOE_OK;
+}
+
+int b200moe_experts(const int32_t* topk_ids, int64_t ids_row_stride, const float* topk_w, int64_t w_row_stride,
+                    const uint8_t* hidden_states, int64_t hidden_row_stride, const float* hidden_scale,
+                    int64_t scale_stride_t, int64_t scale_stride_kb, const uint8_t* w1, const float* w1_scale,
+                    const uint8_t* w2, const float* w2_scale, int T, int e_local, int local_expert_offset,
+                    int hidden, int inter, void* workspace, size_t workspace_bytes, void* out_bf16,
+                    int64_t out_row_stride, void* stream) {
+  if (!topk_ids || !topk_w || !w1 || !w1_scale || !w2 || !w2_scale) return B200MOE_ERR_INVALID_ARGUMENT;
+  if (T > 0 && (!hidden_states || !hidden_scale || !out_bf16)) return B200MOE_ERR_INVALID_ARGUMENT;
+  if (ids_row_stride < kTopK || w_row_stride < kTopK) return B200MOE_ERR_INVALID_ARGUMENT;
+  if (local_expert_offset < 0 || local_expert_offset + e_local > kNumExperts) return B200MOE_ERR_INVALID_ARGUMENT;
+  Workspace ws;
+  int rc = bind_workspace(T, e_local, hidden, inter, workspace, workspace_bytes, &ws);
+  if (rc != B200MOE_OK) return rc;
+  if (hidden_row_stride < hidden || hidden_row_stride % 16 != 0 ||
+      reinterpret_cast<uintptr_t>(hidden_states) % 16 != 0 || reinterpret_cast<uintptr_t>(w1) % 16 != 0 ||
+      reinterpret_cast<uintptr_t>(w2) % 16 != 0 || reinterpret_cast<uintptr_t>(out_bf16) % 8 != 0 ||
+      out_row_stride < hidden || out_row_stride % 4 != 0)
+    return B200MOE_ERR_MISALIGNED;
+  if (T == 0) return B200MOE_OK;
+  int num_sms = 0;
+  if ((rc = ensure_device(&num_sms)) != B200MOE_OK) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+
+  // scratch that accumulates: row maxima and the fp32 output
+  CUDA_TRY(cudaMemsetAsync(ws.base + ws.L.row_amax, 0, (size_t)ws.L.m_cap * 4, st));
+  CUDA_TRY(cudaMemsetAsync(ws.base + ws.L.out_acc, 0, (size_t)T * hidden * 4, st));
+
+  CUDA_TRY(launch_permute(ws, topk_ids, ids_row_stride, topk_w, w_row_stride, hidden_states, hidden_row_stride,
+                          hidden_scale, scale_stride_t, scale_stride_kb, T, e_local, local_expert_offset, hidden,
+                          num_sms, st));
+
+  // small problems get the narrower N tile: more work items to spread over the SMs
+  const int bn = (long long)T * kTopK <= 2048 ? 128 : 256;
+
+  GemmParams g1;
+  memset(&g1, 0, sizeof(g1));
+  if ((rc = make_tmap(&g1.tmap_a, ws.base + ws.L.a_packed, (uint64_t)ws.L.m_cap, (uint64_t)hidden, (uint64_t)hidden,
+                      kTileM)) != B200MOE_OK)
+    return rc;
+  if ((rc = make_tmap(&g1.tmap_b, w1, (uint64_t)e_local * 2 * inter, (uint64_t)hidden, (uint64_t)hidden, bn / 2)) !=
+      B200MOE_OK)
+    return rc;
+  g1.meta = ws.at<int>(ws.L.meta);
+  g1.tile_expert = ws.at<int>(ws.L.tile_expert);
+  g1.row_token = ws.at<int>(ws.L.row_token);
+  g1.a_scale = ws.at<float>(ws.L.a_scale);
+  g1.b_scale = w1_scale;
+  g1.m_cap = ws.L.m_cap;
+  g1.n_per_expert = 2 * inter;
+  g1.kblocks = hidden / kBlockK;
+  g1.n_tiles = inter / (bn / 2);
+  g1.inter = inter;
+  g1.hidden = hidden;
+  g1.act = ws.at<float>(ws.L.act);
+  g1.row_amax = ws.at<unsigned>(ws.L.row_amax);
+  g1.status = ws.at<int>(ws.L.status);
+  CUDA_TRY(launch_grouped_gemm(1, bn, g1, num_sms, st));
+
+  CUDA_TRY(launch_requant(ws, inter, num_sms, st));
+
+  GemmParams g2;
+  memset(&g2, 0, sizeof(g2));
+  if ((rc = make_tmap(&g2.tmap_a, ws.base + ws.L.act_q, (uint64_t)ws.L.m_cap, (uint64_t)inter, (uint64_t)inter,
+                      kTileM)) != B200MOE_OK)
+    return rc;
+  if ((rc = make_tmap(&g2.tmap_b, w2, (uint64_t)e_local * hidden, (uint64_t)inter, (uint64_t)inter, bn / 2)) !=
+      B200MOE_OK)
+    return rc;
+  g2.meta = g1.meta;
+  g2.tile_expert = g1.tile_expert;
+  g2.row_token = g1.row_token;
+  g2.b_scale = w2_scale;
+  g2.m_cap = ws.L.m_cap;
+  g2.n_per_expert = hidden;
+  g2.kblocks = inter / kBlockK;
+  g2.n_tiles = hidden / bn;
+  g2.inter = inter;
+  g2.hidden = hidden;
+  g2.row_scale = ws.at<float>(ws.L.row_scale);
+  g2.row_weight = ws.at<float>(ws.L.row_weight);
+  g2.out_acc = ws.at<float>(ws.L.out_acc);
+  g2.status = g1.status;
+  CUDA_TRY(launch_grouped_gemm(2, bn, g2, num_sms, st));
+
+  CUDA_TRY(launch_finalize(ws.at<float>(ws.L.out_acc), T, hidden, out_bf16, out_row_stride, num_sms, st));
+  return B200MOE_OK;
+}
+
+int b200moe_run(const void* logits, int logits_dtype, const void* bias, int bias_dtype, const uint8_t* hidden_states,
+                int64_t hidden_row_stride, const float* hidden_scale, int64_t scale_stride_t,
+                int64_t scale_stride_kb, const uint8_t* w1, const float* w1_scale, const uint8_t* w2,
+                const float* w2_scale, int T, int e_local, int local_expert_offset, float routed_scaling_factor,
+                int hidden, int inter, void* workspace, size_t workspace_bytes, void* out_bf16,
+                int64_t out_row_stride, void* stream) {
+  Workspace ws;
+  int rc = bind_workspace(T, e_local, hidden, inter, workspace, workspace_bytes, &ws);
+  if (rc != B200MOE_OK) return rc;
+  if (T == 0) return B200MOE_OK;
+  int32_t* ids = ws.at<int32_t>(ws.L.topk_ids);
+  float* w = ws.at<float>(ws.L.topk_w);
+  rc = b200moe_route(logits, logits_dtype, bias, bias_dtype, T, routed_scaling_factor, local_expert_offset, e_local,
+                     hidden, inter, ids, w, workspace, workspace_bytes, stream);
+  if (rc != B200MOE_OK) return rc;
+  return b200moe_experts(ids, kTopK, w, kTopK, hidden_states, hidden_row_stride, hidden_scale, scale_stride_t,
+                         scale_stride_kb, w1, w1_scale, w2, w2_scale, T, e_local, local_expert_offset, hidden, inter,
+                         workspace, workspace_bytes, out_bf16, out_row_stride, stream);
+}
+
+int b200moe_read_status(const void* workspace, void* stream, int32_t* detail) {
+  if (!workspace) return B200MOE_ERR_INVALID_ARGUMENT;
+  int32_t host[4] = {0, 0, 0, 0};
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  CUDA_TRY(cudaMemcpyAsync(host, workspace, sizeof(host), cudaMemcpyDeviceToHost, st));
+  CUDA_TRY(cudaStreamSynchronize(st));
+  if (detail) memcpy(detail, host, sizeof(host));
+  return host[kStatusCode];
+}
+
+int b200moe_ep_pack(const int32_t* topk_ids, const float* topk_w, const uint8_t* hidden_states,
+                    int64_t hidden_row_stride, const float* hidden_scale, int64_t scale_stride_t,
+                    int64_t scale_stride_kb, int T, int hidden, int world, uint8_t* send_rows, int32_t* dest_counts,
+                    int32_t* send_slot, void* stream) {
+  if (!topk_ids || !topk_w || !send_rows || !dest_counts || !send_slot || T < 0) return B200MOE_ERR_INVALID_ARGUMENT;
+  if (T > 0 && (!hidden_states || !hidden_scale)) return B200MOE_ERR_INVALID_ARGUMENT;
+  if (world != 1 && world != 2 && world != 4 && world != 8) return B200MOE_ERR_UNSUPPORTED_SHAPE;
+  if (hidden < 512 || hidden % 512 != 0) return B200MOE_ERR_UNSUPPORTED_SHAPE;   // keeps send rows 16-byte aligned
+  if (hidden_row_stride % 16 != 0 || reinterpret_cast<uintptr_t>(hidden_states) % 16 != 0 ||
+      reinterpret_cast<uintptr_t>(send_rows) % 16 != 0)
+    return B200MOE_ERR_MISALIGNED;
+  int num_sms = 0;
+  int rc = ensure_device(&num_sms);
+  if (rc != B200MOE_OK) return rc;
+  CUDA_TRY(launch_ep_pack(topk_ids, topk_w, hidden_states, hidden_row_stride, hidden_scale, scale_stride_t,
+                          scale_stride_kb, T, hidden, world, send_rows, dest_counts, send_slot, num_sms,
+                          reinterpret_cast<cudaStream_t>(stream)));
+  return B200MOE_OK;
+}
+
+int b200moe_ep_combine(const void* returned_bf16, const int32_t* send_slot, const int32_t* dest_counts, int T,
+                       int hidden, int world, void* out_bf16, void* stream) {
+  if (!returned_bf16 || !send_slot || !dest_counts || !out_bf16 || T < 0) return B200MOE_ERR_INVALID_ARGUMENT;
+  if (world != 1 && world != 2 && world != 4 && world != 8) return B200MOE_ERR_UNSUPPORTED_SHAPE;
+  if (hidden < 8 || hidden % 8 != 0) return B200MOE_ERR_UNSUPPORTED_SHAPE;
+  if (reinterpret_cast<uintptr_t>(returned_bf16) % 16 != 0 || reinterpret_cast<uintptr_t>(out_bf16) % 16 != 0)
+    return B200MOE_ERR_MISALIGNED;
+  int num_sms = 0;
+  int rc = ensure_device(&num_sms);
+  if (rc != B200MOE_OK) return rc;
+  CUDA_TRY(launch_ep_combine(returned_bf16, send_slot, dest_counts, T, hidden, world, out_bf16, num_sms,
+                             reinterpret_cast<cudaStream_t>(stream)));
+  return B200MOE_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,297 @@
+// Persistent grouped FP8 GEMMs on tcgen05 tensor cores with exact fp32 block scales.
+//
+// Replaces the reference's CUTLASS grouped GEMM `moe_blockwise_grouped_mm_v2`
+// (solution/python/moe_gemm.cu:310-340, 418-654) plus, in the epilogues, its
+// `swiglu_fp8_requant_kernel` front half (solution/python/moe_fused.cu:131-196) and its
+// combine kernels (`weighted_scatter_kernel` moe_fused.cu:490-517,
+// `reduce_scatter_from_2d_perm_kernel` moe_fused.cu:346-393).
+//
+// One CTA per SM walks work items (M tile of 128 packed rows, N tile of BN weight rows).
+// Per 128-wide K block (= one fp32 scale block, = one 128-byte swizzled TMA row):
+//   warp 0     TMA producer: A box 128x128 B and two B boxes (BN/2)x128 B into a smem ring
+//   warp 1     issues 4 tcgen05.mma (K=32 each) into one of two TMEM accumulators, starting
+//              from zero, so each accumulator holds the raw e4m3 dot product of one K block
+//   warps 2-9  read that accumulator back (tcgen05.ld) and fold it into fp32 registers as
+//              acc += (a_scale * b_scale) * partial  -- the block scales are arbitrary fp32
+//              numbers, so they cannot ride on the MMA itself
+// GEMM1 pairs gate rows [n, n+BN/2) with up rows [inter+n, ...) in one tile, so the epilogue
+// computes g*silu(u) in registers, stores fp32 activations and the row maximum.
+// GEMM2's epilogue multiplies by (row requant scale * routing weight) and adds the row into
+// the token's fp32 output with vector reductions.
+//
+// Every wait is bounded (see mbar_wait); on a timeout the CTA drains and frees its TMEM.
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace b200moe {
+
+namespace {
+
+constexpr int kGemmThreads = 320;
+constexpr int kEpiWarps = 8;
+constexpr int kABytes = kTileM * kBlockK;   // 16 KiB
+
+template <int BN> struct TileCfg {
+  static constexpr int kBBytes = BN * kBlockK;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kBarBytes = 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;   // + alignment slack
+  static constexpr int kColsPerThread = BN / 2;
+  static constexpr int kChunks = kColsPerThread / 32;
+};
+
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  float sig = 1.0f / (1.0f + __expf(-u));
+  return g * (u * sig);
+}
+
+template <int MODE, int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
+  using Cfg = TileCfg<BN>;
+  constexpr int S = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes);
+  const uint32_t bar_full = smem_u32(bars);              // S barriers: stage filled by TMA
+  const uint32_t bar_empty = bar_full + 8 * S;           // S barriers: stage consumed by the MMAs
+  const uint32_t bar_tfull = bar_empty + 8 * S;          // 2 barriers: accumulator written
+  const uint32_t bar_tempty = bar_tfull + 16;            // 2 barriers: accumulator read back
+  const uint32_t bar_drain = bar_tempty + 16;            // 1 barrier: all MMAs retired (teardown)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 5);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(bar_tfull + 8 * b, 1);
+      mbar_init(bar_tempty + 8 * b, kEpiWarps);
+    }
+    mbar_init(bar_drain, 1);
+    abort_flag[0] = 0;
+    abort_flag[1] = 0;   // never set by others: the teardown waits ignore an abort
+    fence_mbar_init();
+    tma_prefetch_desc(&p.tmap_a);
+    tma_prefetch_desc(&p.tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int m_tiles = p.meta[0];
+  const int total_items = m_tiles * p.n_tiles;
+  const int kblocks = p.kblocks;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool alive = true;
+      for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x) {
+        const int m_tile = w / p.n_tiles, n_tile = w % p.n_tiles;
+        const int e = p.tile_expert[m_tile];
+        int brow0, brow1;
+        if (MODE == 1) {
+          brow0 = e * p.n_per_expert + n_tile * (BN / 2);
+          brow1 = brow0 + p.inter;
+        } else {
+          brow0 = e * p.n_per_expert + n_tile * BN;
+          brow1 = brow0 + BN / 2;
+        }
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const uint32_t s = it % S, ph = (it / S) & 1u;
+          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status, 1)) { alive = false; break; }
+          const uint32_t full = bar_full + 8 * s;
+          const uint32_t a_dst = smem_base + s * Cfg::kStageBytes;
+          mbar_arrive_expect_tx(full, Cfg::kStageBytes);
+          tma_load_2d(a_dst, &p.tmap_a, kb * kBlockK, m_tile * kTileM, full);
+          tma_load_2d(a_dst + kABytes, &p.tmap_b, kb * kBlockK, brow0, full);
+          tma_load_2d(a_dst + kABytes + (BN / 2) * kBlockK, &p.tmap_b, kb * kBlockK, brow1, full);
+        }
+      }
+      // Copies still in flight must land before the CTA's shared memory is released.
+      const uint32_t first = it > (uint32_t)S ? it - S : 0u;
+      for (uint32_t j = first; j < it; ++j)
+        (void)mbar_wait(bar_full + 8 * (j % S), (j / S) & 1u, abort_flag + 1, p.status, 6);
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_e4m3(kTileM, BN);
+      uint32_t it = 0;
+      bool alive = true;
+      for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x) {
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const uint32_t s = it % S, ph = (it / S) & 1u;
+          const uint32_t b = it & 1u, bph = (it >> 1) & 1u;
+          if (!mbar_wait(bar_tempty + 8 * b, bph ^ 1u, abort_flag, p.status, 2)) { alive = false; break; }
+          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 3)) { alive = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + s * Cfg::kStageBytes;
+          const uint32_t b_addr = a_addr + kABytes;
+          const uint32_t d_addr = tmem_base + b * BN;
+#pragma unroll
+          for (int k4 = 0; k4 < kBlockK / 32; ++k4) {
+            tc_mma_f8(d_addr, make_kmajor_sw128_desc(a_addr + k4 * 32), make_kmajor_sw128_desc(b_addr + k4 * 32),
+                      idesc, k4 > 0 ? 1u : 0u);
+          }
+          tc_commit(bar_empty + 8 * s);
+          tc_commit(bar_tfull + 8 * b);
+        }
+      }
+      // All MMAs must retire before TMEM is freed.
+      tc_commit(bar_drain);
+      (void)mbar_wait(bar_drain, 0u, abort_flag + 1, p.status, 5);
+    }
+  } else {
+    // ------------------------------ promotion + epilogue ------------------------------
+    const int ew = warp - 2;
+    const int q = warp & 3;        // TMEM lane quarter this warp may read
+    const int h = ew >> 2;         // which half of the tile's columns
+    constexpr int CPT = Cfg::kColsPerThread;
+    constexpr int CH = Cfg::kChunks;
+    uint32_t it = 0;
+    bool alive = true;
+    for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x) {
+      const int m_tile = w / p.n_tiles, n_tile = w % p.n_tiles;
+      const int e = p.tile_expert[m_tile];
+      const int row = m_tile * kTileM + q * 32 + lane;
+      const int tok = p.row_token[row];
+      float acc[CPT];
+#pragma unroll
+      for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
+
+      // scale pointers
+      const float* sa_ptr = nullptr;
+      const float* sb0_ptr;
+      const float* sb1_ptr = nullptr;
+      const int nblk_per_expert = p.n_per_expert / kBlockK;
+      if (MODE == 1) {
+        sa_ptr = p.a_scale + row;
+        const int gcol0 = n_tile * (BN / 2) + h * (BN / 4);          // first gate row of this thread
+        sb0_ptr = p.b_scale + ((size_t)e * nblk_per_expert + gcol0 / kBlockK) * kblocks;
+        sb1_ptr = p.b_scale + ((size_t)e * nblk_per_expert + (p.inter + gcol0) / kBlockK) * kblocks;
+      } else {
+        const int col0 = n_tile * BN + h * (BN / 2);
+        sb0_ptr = p.b_scale + ((size_t)e * nblk_per_expert + col0 / kBlockK) * kblocks;
+      }
+      float sa_n = MODE == 1 ? sa_ptr[0] : 1.f;
+      float sb0_n = sb0_ptr[0];
+      float sb1_n = MODE == 1 ? sb1_ptr[0] : 0.f;
+
+      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        const uint32_t b = it & 1u, bph = (it >> 1) & 1u;
+        const float sc0 = sa_n * sb0_n;
+        const float sc1 = sa_n * sb1_n;
+        if (kb + 1 < kblocks) {
+          if (MODE == 1) {
+            sa_n = sa_ptr[(size_t)(kb + 1) * p.m_cap];
+            sb1_n = sb1_ptr[kb + 1];
+          }
+          sb0_n = sb0_ptr[kb + 1];
+        }
+        bool ok = mbar_wait(bar_tfull + 8 * b, bph, abort_flag, p.status, 4);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) { alive = false; break; }
+        tc_fence_after();
+        const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + b * BN;
+#pragma unroll
+        for (int c = 0; c < CH; ++c) {
+          uint32_t col;
+          float sc;
+          if (MODE == 1) {
+            const bool up = c >= CH / 2;
+            col = (up ? BN / 2 : 0) + h * (BN / 4) + (up ? c - CH / 2 : c) * 32;
+            sc = up ? sc1 : sc0;
+          } else {
+            col = h * (BN / 2) + c * 32;
+            sc = sc0;
+          }
+          uint32_t r[32];
+          tmem_ld_32x32(t_row + col, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(__uint_as_float(r[j]), sc, acc[c * 32 + j]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
+      }
+      if (!alive) break;
+
+      if (tok >= 0) {
+        if (MODE == 1) {
+          // acc[0 .. CPT/2) = gate columns, acc[CPT/2 .. CPT) = matching up columns
+          constexpr int HALF = CPT / 2;
+          float* dst = p.act + (size_t)row * p.inter + n_tile * (BN / 2) + h * (BN / 4);
+          float amax = 0.f;
+#pragma unroll
+          for (int j = 0; j < HALF; j += 4) {
+            float4 v;
+            v.x = silu_mul(acc[j + 0], acc[HALF + j + 0]);
+            v.y = silu_mul(acc[j + 1], acc[HALF + j + 1]);
+            v.z = silu_mul(acc[j + 2], acc[HALF + j + 2]);
+            v.w = silu_mul(acc[j + 3], acc[HALF + j + 3]);
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+            *reinterpret_cast<float4*>(dst + j) = v;
+          }
+          atomicMax(p.row_amax + row, __float_as_uint(amax));
+        } else {
+          const float rs = p.row_scale[row] * p.row_weight[row];
+          float* dst = p.out_acc + (size_t)tok * p.hidden + n_tile * BN + h * (BN / 2);
+#pragma unroll
+          for (int j = 0; j < CPT; j += 4)
+            red_add_v4(dst + j, acc[j] * rs, acc[j + 1] * rs, acc[j + 2] * rs, acc[j + 3] * rs);
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+template <int MODE, int BN>
+cudaError_t launch_one(const GemmParams& p, int num_sms, cudaStream_t stream) {
+  grouped_gemm_kernel<MODE, BN><<<num_sms, kGemmThreads, TileCfg<BN>::kSmemBytes, stream>>>(p);
+  return cudaGetLastError();
+}
+
+template <int MODE, int BN>
+cudaError_t configure_one() {
+  return cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              TileCfg<BN>::kSmemBytes);
+}
+
+}  // namespace
+
+cudaError_t configure_grouped_gemm() {
+  cudaError_t e;
+  if ((e = configure_one<1, 128>()) != cudaSuccess) return e;
+  if ((e = configure_one<1, 256>()) != cudaSuccess) return e;
+  if ((e = configure_one<2, 128>()) != cudaSuccess) return e;
+  if ((e = configure_one<2, 256>()) != cudaSuccess) return e;
+  return cudaSuccess;
+}
+
+cudaError_t launch_grouped_gemm(int mode, int bn, const GemmParams& p, int num_sms, cudaStream_t stream) {
+  if (mode == 1) return bn == 128 ? launch_one<1, 128>(p, num_sms, stream) : launch_one<1, 256>(p, num_sms, stream);
+  return bn == 128 ? launch_one<2, 128>(p, num_sms, stream) : launch_one<2, 256>(p, num_sms, stream);
+}
+
+}  // namespace b200moe

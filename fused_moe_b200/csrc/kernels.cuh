@@ -1,0 +1,59 @@
+// Launchers of the device kernels (one translation unit each), called from capi.cu.
+#pragma once
+
+#include "common.cuh"
+
+namespace b200moe {
+
+cudaError_t launch_route(const void* logits, int logits_dtype, const void* bias, int bias_dtype, int T, float rsf,
+                         int local_off, int e_local, int32_t* ids, float* w, int* chunk_counts, int num_sms,
+                         cudaStream_t stream);
+
+cudaError_t launch_count(const int32_t* ids, long long row_stride, int T, int local_off, int e_local,
+                         int* chunk_counts, int num_sms, cudaStream_t stream);
+
+cudaError_t launch_permute(const Workspace& ws, const int32_t* ids, long long ids_stride, const float* w,
+                           long long w_stride, const uint8_t* hidden, long long hidden_row_stride,
+                           const float* hscale, long long sstride_t, long long sstride_kb, int T, int e_local,
+                           int local_off, int hidden_dim, int num_sms, cudaStream_t stream);
+
+// Arguments of the two grouped GEMMs.  `tmap_a` covers the packed rows [m_cap][K],
+// `tmap_b` the weights viewed as [e_local * N][K]; both e4m3, 128-byte swizzled boxes.
+struct GemmParams {
+  CUtensorMap tmap_a;
+  CUtensorMap tmap_b;
+  const int* meta;          // [0] = number of 128-row M tiles
+  const int* tile_expert;   // expert of each M tile
+  const int* row_token;     // token of each packed row, -1 for padding
+  const float* a_scale;     // GEMM1: [K/128][m_cap] activation scales
+  const float* b_scale;     // [e_local][N/128][K/128] weight scales
+  int m_cap;
+  int n_per_expert;         // weight rows per expert (GEMM1: 2*inter, GEMM2: hidden)
+  int kblocks;              // K / 128
+  int n_tiles;              // N tiles per M tile
+  int inter;
+  int hidden;
+  float* act;               // GEMM1 out: [m_cap][inter] fp32
+  unsigned* row_amax;       // GEMM1 out: bits of max |act| per row
+  const float* row_scale;   // GEMM2 in: requantisation scale per row
+  const float* row_weight;  // GEMM2 in: routing weight per row
+  float* out_acc;           // GEMM2 out: [T][hidden] fp32, accumulated with red.add
+  int* status;
+};
+
+// mode 1: GEMM1 + SwiGLU + row amax; mode 2: GEMM2 + weighted combine.  bn: 128 or 256.
+cudaError_t launch_grouped_gemm(int mode, int bn, const GemmParams& p, int num_sms, cudaStream_t stream);
+cudaError_t configure_grouped_gemm();   // opt-in shared memory sizes, once per process and device
+
+cudaError_t launch_requant(const Workspace& ws, int inter, int num_sms, cudaStream_t stream);
+cudaError_t launch_finalize(const float* out_acc, int T, int hidden, void* out_bf16, long long out_row_stride,
+                            int num_sms, cudaStream_t stream);
+
+cudaError_t launch_ep_pack(const int32_t* ids, const float* w, const uint8_t* hidden, long long hidden_row_stride,
+                           const float* hscale, long long sstride_t, long long sstride_kb, int T, int hidden_dim,
+                           int world, uint8_t* send_rows, int32_t* dest_counts, int32_t* send_slot, int num_sms,
+                           cudaStream_t stream);
+cudaError_t launch_ep_combine(const void* returned_bf16, const int32_t* send_slot, const int32_t* dest_counts, int T,
+                              int hidden_dim, int world, void* out_bf16, int num_sms, cudaStream_t stream);
+
+}  // namespace b200moe

@@ -1,0 +1,158 @@
+// Permutation of (token, k) pairs into per-expert row segments padded to 128-row tiles.
+//
+// Replaces the reference's `exclusive_scan_kernel`, `dispatch_place_kernel`,
+// `fused_dispatch_single_block_kernel` (solution/python/moe_fused.cu:888-1051) and
+// `fused_gather_hidden_scales_kernel` (moe_fused.cu:736-768).  Unlike the reference's
+// atomic cursor, placement is stable by token id, so the packed order (and every later
+// intermediate) is identical from run to run.
+//
+//   scan   : per-expert totals from the per-chunk histogram, 128-padded segment starts,
+//            the M-tile -> expert table, per-chunk bases, padding rows marked -1
+//   place  : one block per 256-token chunk; a warp walks an expert's tokens in order
+//   gather : one warp per packed row copies the e4m3 row and its 1x128 scales
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace b200moe {
+
+namespace {
+
+__global__ void __launch_bounds__(256)
+scan_kernel(Workspace ws, int e_local, int n_chunks) {
+  __shared__ int s_scan[256];
+  const int e = threadIdx.x;
+  int* chunk_counts = ws.at<int>(ws.L.chunk_counts);
+  int* chunk_base = ws.at<int>(ws.L.chunk_base);
+  int total = 0;
+  if (e < e_local) {
+    for (int c = 0; c < n_chunks; ++c) {
+      chunk_base[c * e_local + e] = total;
+      total += chunk_counts[c * e_local + e];
+    }
+  }
+  int padded = (total + kTileM - 1) / kTileM * kTileM;
+  s_scan[e] = padded;
+  __syncthreads();
+  // inclusive Hillis-Steele scan over 256 entries
+  for (int off = 1; off < 256; off <<= 1) {
+    int v = e >= off ? s_scan[e - off] : 0;
+    __syncthreads();
+    s_scan[e] += v;
+    __syncthreads();
+  }
+  int row0 = s_scan[e] - padded;
+  int* expert_row0 = ws.at<int>(ws.L.expert_row0);
+  int* expert_count = ws.at<int>(ws.L.expert_count);
+  int* tile_expert = ws.at<int>(ws.L.tile_expert);
+  int* row_token = ws.at<int>(ws.L.row_token);
+  if (e < e_local) {
+    expert_row0[e] = row0;
+    expert_count[e] = total;
+    for (int t = row0 / kTileM; t < (row0 + padded) / kTileM; ++t) tile_expert[t] = e;
+    for (int r = row0 + total; r < row0 + padded; ++r) row_token[r] = -1;
+  }
+  // totals: rows with a local expert (for reporting) and padded rows
+  __shared__ int s_rows;
+  if (e == 0) s_rows = 0;
+  __syncthreads();
+  if (e < e_local && total) atomicAdd(&s_rows, total);
+  __syncthreads();
+  if (e == 0) {
+    int padded_total = s_scan[255];
+    expert_row0[e_local] = padded_total;
+    int* meta = ws.at<int>(ws.L.meta);
+    meta[0] = padded_total / kTileM;
+    meta[1] = padded_total;
+    meta[2] = s_rows;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+place_kernel(Workspace ws, const int32_t* __restrict__ ids, long long ids_stride,
+             const float* __restrict__ w, long long w_stride, int T, int local_off, int e_local) {
+  __shared__ int s_ids[kTopK][kChunkTokens];   // [k][token]: conflict-free when lanes walk tokens
+  const int c = blockIdx.x;
+  const int t0 = c * kChunkTokens;
+  for (int i = threadIdx.x; i < kChunkTokens * kTopK; i += blockDim.x) {
+    int tl = i / kTopK, k = i % kTopK;
+    int t = t0 + tl;
+    s_ids[k][tl] = t < T ? ids[(size_t)t * ids_stride + k] : -1;
+  }
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int* chunk_counts = ws.at<int>(ws.L.chunk_counts);
+  const int* chunk_base = ws.at<int>(ws.L.chunk_base);
+  const int* expert_row0 = ws.at<int>(ws.L.expert_row0);
+  int* row_token = ws.at<int>(ws.L.row_token);
+  float* row_weight = ws.at<float>(ws.L.row_weight);
+  for (int e = warp; e < e_local; e += nwarps) {
+    if (chunk_counts[c * e_local + e] == 0) continue;
+    int pos = expert_row0[e] + chunk_base[c * e_local + e];
+    const int want = e + local_off;
+    for (int sub = 0; sub < kChunkTokens / 32; ++sub) {
+      int tl = sub * 32 + lane;
+      int kf = -1;
+#pragma unroll
+      for (int k = 0; k < kTopK; ++k)
+        if (s_ids[k][tl] == want) kf = k;
+      uint32_t hit = __ballot_sync(0xffffffffu, kf >= 0);
+      if (kf >= 0) {
+        int r = pos + __popc(hit & ((1u << lane) - 1u));
+        int t = t0 + tl;
+        row_token[r] = t;
+        row_weight[r] = w[(size_t)t * w_stride + kf];
+      }
+      pos += __popc(hit);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+gather_kernel(Workspace ws, const uint8_t* __restrict__ hidden, long long hidden_row_stride,
+              const float* __restrict__ hscale, long long sstride_t, long long sstride_kb, int hidden_dim) {
+  const int lane = threadIdx.x & 31;
+  const int warps_per_block = blockDim.x >> 5;
+  const int rows = ws.at<int>(ws.L.meta)[1];
+  const int* row_token = ws.at<int>(ws.L.row_token);
+  uint8_t* a_packed = ws.at<uint8_t>(ws.L.a_packed);
+  float* a_scale = ws.at<float>(ws.L.a_scale);
+  const int m_cap = ws.L.m_cap;
+  const int vecs = hidden_dim / 16;
+  const int kblocks = hidden_dim / kBlockK;
+  for (int m = blockIdx.x * warps_per_block + (threadIdx.x >> 5); m < rows; m += gridDim.x * warps_per_block) {
+    int t = row_token[m];
+    if (t < 0) continue;
+    const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)t * hidden_row_stride);
+    uint4* dst = reinterpret_cast<uint4*>(a_packed + (size_t)m * hidden_dim);
+    for (int v = lane; v < vecs; v += 32) dst[v] = __ldg(src + v);
+    for (int kb = lane; kb < kblocks; kb += 32)
+      a_scale[(size_t)kb * m_cap + m] = hscale[(size_t)t * sstride_t + (size_t)kb * sstride_kb];
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_permute(const Workspace& ws, const int32_t* ids, long long ids_stride, const float* w,
+                           long long w_stride, const uint8_t* hidden, long long hidden_row_stride,
+                           const float* hscale, long long sstride_t, long long sstride_kb, int T, int e_local,
+                           int local_off, int hidden_dim, int num_sms, cudaStream_t stream) {
+  const int n_chunks = (T + kChunkTokens - 1) / kChunkTokens;
+  scan_kernel<<<1, 256, 0, stream>>>(ws, e_local, n_chunks);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return err;
+  if (n_chunks > 0) {
+    place_kernel<<<n_chunks, 256, 0, stream>>>(ws, ids, ids_stride, w, w_stride, T, local_off, e_local);
+    err = cudaGetLastError();
+    if (err != cudaSuccess) return err;
+    long long cap_rows = ws.L.m_cap;
+    int blocks = (int)((cap_rows + 7) / 8);
+    int cap = num_sms * 8;
+    if (blocks > cap) blocks = cap;
+    gather_kernel<<<blocks, 256, 0, stream>>>(ws, hidden, hidden_row_stride, hscale, sstride_t, sstride_kb,
+                                              hidden_dim);
+    err = cudaGetLastError();
+  }
+  return err;
+}
+
+}  // namespace b200moe

@@ -1,0 +1,160 @@
+// Routing (DeepSeek-V3 no-aux) and the per-chunk histogram of local experts.
+//
+// Replaces the reference's `fused_route_topk_kernel` (solution/python/moe_fused.cu:568-698)
+// and `dispatch_count_kernel` (moe_fused.cu:866-881).  Semantics follow the reference's
+// torch check (experiments/fast_bench/correctness_bench.py:47-61): fp32 logits are used as
+// given, group scores count equal values with multiplicity, and every selection breaks ties
+// toward the lowest index.
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace b200moe {
+
+namespace {
+
+// Monotone map fp32 -> uint32 (a < b  <=>  key(a) < key(b), with -0 < +0 adjacent).
+__device__ __forceinline__ uint32_t order_key(float v) {
+  uint32_t u = __float_as_uint(v);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+__device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) {
+    unsigned long long o = __shfl_xor_sync(0xffffffffu, v, off);
+    v = o > v ? o : v;
+  }
+  return v;
+}
+
+// sigmoid evaluated in fp64 and rounded once to fp32: within one rounding of the exact
+// value, so expert ids can differ from another correctly evaluated sigmoid only when two
+// competing scores are within an fp32 ulp of each other.
+__device__ __forceinline__ float sigmoid_round_once(float x) {
+  return (float)(1.0 / (1.0 + exp(-(double)x)));
+}
+
+constexpr int kRouteWarps = 8;
+
+__global__ void __launch_bounds__(kRouteWarps * 32)
+route_kernel(const void* __restrict__ logits, int logits_dtype, const void* __restrict__ bias, int bias_dtype,
+             int T, float rsf, int local_off, int e_local,
+             int32_t* __restrict__ topk_ids, float* __restrict__ topk_w, int* __restrict__ chunk_counts) {
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  // Lane L owns expert g*32+L of every group g, so a group reduction is a warp reduction.
+  float b[kNumGroups];
+#pragma unroll
+  for (int g = 0; g < kNumGroups; ++g) b[g] = load_as_float(bias, bias_dtype, g * 32 + lane);
+
+  for (int t = blockIdx.x * kRouteWarps + warp; t < T; t += gridDim.x * kRouteWarps) {
+    float s[kNumGroups];
+    uint32_t key[kNumGroups];   // order key of sigmoid + bias
+    float gscore = 0.f;         // lane g (< 8) keeps the score of group g
+#pragma unroll
+    for (int g = 0; g < kNumGroups; ++g) {
+      float x = load_as_float(logits, logits_dtype, (size_t)t * kNumExperts + g * 32 + lane);
+      s[g] = sigmoid_round_once(x);
+      float swb = s[g] + b[g];
+      key[g] = order_key(swb);
+      // top-2 with multiplicity: take the best (value, lane) pair, drop that one lane, take the best again
+      unsigned long long mine = ((unsigned long long)key[g] << 32) | (uint32_t)(31 - lane);
+      unsigned long long best = warp_max_u64(mine);
+      unsigned long long rest = warp_max_u64(mine == best ? 0ull : mine);
+      uint32_t k1 = (uint32_t)(best >> 32), k2 = (uint32_t)(rest >> 32);
+      float v1 = __uint_as_float((k1 & 0x80000000u) ? (k1 & 0x7fffffffu) : ~k1);
+      float v2 = __uint_as_float((k2 & 0x80000000u) ? (k2 & 0x7fffffffu) : ~k2);
+      float sc = v1 + v2;
+      if (lane == g) gscore = sc;
+    }
+    // top-4 groups: four rounds of (score, lowest index) maxima over lanes 0..7
+    unsigned long long gk = lane < kNumGroups
+        ? (((unsigned long long)order_key(gscore) << 32) | (uint32_t)(kNumGroups - 1 - lane) | 0x100u)
+        : 0ull;
+    uint32_t group_mask = 0;
+#pragma unroll
+    for (int r = 0; r < kTopKGroups; ++r) {
+      unsigned long long best = warp_max_u64(gk);
+      int g = kNumGroups - 1 - (int)(best & 0xffu);
+      group_mask |= 1u << g;
+      if (lane == g) gk = 0ull;
+    }
+    // top-8 experts among the kept groups; a taken or masked candidate has key 0
+    unsigned long long cand[kNumGroups];
+#pragma unroll
+    for (int g = 0; g < kNumGroups; ++g) {
+      uint32_t id = g * 32 + lane;
+      cand[g] = ((group_mask >> g) & 1u)
+          ? (((unsigned long long)key[g] << 32) | (uint32_t)(kNumExperts - 1 - id) | 0x100u)
+          : 0ull;
+    }
+    float ssum = 0.f;
+    float my_s = 0.f;   // lane k keeps s of the k-th winner
+    int my_id = 0;
+#pragma unroll
+    for (int k = 0; k < kTopK; ++k) {
+      unsigned long long loc = cand[0];
+#pragma unroll
+      for (int g = 1; g < kNumGroups; ++g) loc = cand[g] > loc ? cand[g] : loc;
+      unsigned long long best = warp_max_u64(loc);
+      int id = kNumExperts - 1 - (int)(best & 0xffu);
+      int wl = id & 31, wg = id >> 5;
+      float sw = 0.f;
+#pragma unroll
+      for (int g = 0; g < kNumGroups; ++g) {
+        if (g == wg) {
+          sw = s[g];
+          if (lane == wl) cand[g] = 0ull;
+        }
+      }
+      sw = __shfl_sync(0xffffffffu, sw, wl);
+      ssum += sw;   // left-to-right fp32 sum in rank order, identical on every lane
+      if (lane == k) { my_s = sw; my_id = id; }
+    }
+    float factor = rsf / (ssum + 1e-20f);
+    if (lane < kTopK) {
+      topk_ids[(size_t)t * kTopK + lane] = my_id;
+      topk_w[(size_t)t * kTopK + lane] = my_s * factor;
+      int le = my_id - local_off;
+      if (le >= 0 && le < e_local) atomicAdd(&chunk_counts[(t / kChunkTokens) * e_local + le], 1);
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+count_kernel(const int32_t* __restrict__ ids, long long row_stride, int T, int local_off, int e_local,
+             int* __restrict__ chunk_counts) {
+  long long n = (long long)T * kTopK;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    int t = (int)(i / kTopK), k = (int)(i % kTopK);
+    int le = ids[(size_t)t * row_stride + k] - local_off;
+    if (le >= 0 && le < e_local) atomicAdd(&chunk_counts[(t / kChunkTokens) * e_local + le], 1);
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_route(const void* logits, int logits_dtype, const void* bias, int bias_dtype, int T, float rsf,
+                         int local_off, int e_local, int32_t* ids, float* w, int* chunk_counts, int num_sms,
+                         cudaStream_t stream) {
+  if (T <= 0) return cudaSuccess;
+  int blocks = (T + kRouteWarps - 1) / kRouteWarps;
+  int cap = num_sms * 8;
+  if (blocks > cap) blocks = cap;
+  route_kernel<<<blocks, kRouteWarps * 32, 0, stream>>>(logits, logits_dtype, bias, bias_dtype, T, rsf, local_off,
+                                                       e_local, ids, w, chunk_counts);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_count(const int32_t* ids, long long row_stride, int T, int local_off, int e_local,
+                         int* chunk_counts, int num_sms, cudaStream_t stream) {
+  if (T <= 0) return cudaSuccess;
+  long long n = (long long)T * kTopK;
+  int blocks = (int)((n + 255) / 256);
+  int cap = num_sms * 8;
+  if (blocks > cap) blocks = cap;
+  count_kernel<<<blocks, 256, 0, stream>>>(ids, row_stride, T, local_off, e_local, chunk_counts);
+  return cudaGetLastError();
+}
+
+}  // namespace b200moe

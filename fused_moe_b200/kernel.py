@@ -1,0 +1,242 @@
+"""Host side of the fused MoE layer: the reference's entry point, re-hosted on the C ABI.
+
+``run`` / ``kernel`` / ``custom_kernel`` keep the reference's positional signature
+(solution/python/kernel.py:575-648):
+
+    run(routing_logits, routing_bias, hidden_states, hidden_states_scale,
+        gemm1_weights, gemm1_weights_scale, gemm2_weights, gemm2_weights_scale,
+        local_expert_offset, routed_scaling_factor) -> bf16 [T, hidden]
+
+Differences a caller can observe, all documented at the boundary:
+* fp32 routing logits are used as given (the reference casts them to bf16, kernel.py:146);
+* the result is written into a buffer owned by this module and reused by the next call
+  with the same shapes, exactly as the reference does (kernel.py:251, 636) - pass
+  ``out=`` to write into a tensor of your own instead;
+* shapes the CUDA library does not support raise ``MoEError`` instead of asserting.
+
+torch is used for tensors, streams and the workspace allocation only; every kernel
+is in ``libb200moe.so``.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import _capi
+from ._capi import MoEError  # noqa: F401  (re-exported)
+
+E_GLOBAL = 256
+TOP_K = 8
+BLOCK = 128
+
+
+class Workspace:
+    """Device scratch of one (device, T capacity, e_local, hidden, inter) problem.
+
+    Replaces the reference's per-shape dict of ~40 tensors (kernel.py:208-329): one
+    allocation, carved by the library (``b200moe_workspace_layout``).
+    """
+
+    def __init__(self, device: torch.device, T: int, e_local: int, hidden: int, inter: int):
+        self.device, self.T, self.e_local, self.hidden, self.inter = device, T, e_local, hidden, inter
+        self.layout = _capi.workspace_layout(T, e_local, hidden, inter)
+        self.nbytes = int(self.layout.total_bytes)
+        # zero-filled once so that padding rows never hold NaN bit patterns from a previous owner
+        self.buffer = torch.zeros(self.nbytes + 256, dtype=torch.uint8, device=device)
+        self.ptr = (self.buffer.data_ptr() + 255) // 256 * 256
+        self._skip = self.ptr - self.buffer.data_ptr()
+        self.out = torch.empty((max(T, 1), hidden), dtype=torch.bfloat16, device=device)
+
+    def view(self, name: str, dtype: torch.dtype, shape) -> torch.Tensor:
+        """A typed view of one intermediate (tests and tools)."""
+        off = int(getattr(self.layout, name)) + self._skip
+        n = 1
+        for s in shape:
+            n *= int(s)
+        nb = n * torch.empty((), dtype=dtype).element_size()
+        return self.buffer[off:off + nb].view(dtype).view(*shape)
+
+    def read_status(self, stream_ptr: int = 0):
+        detail = (C.c_int32 * 4)()
+        code = _capi.lib().b200moe_read_status(self.ptr, stream_ptr, detail)
+        return code, list(detail)
+
+
+_workspaces: Dict[Tuple, Workspace] = {}
+
+
+def get_workspace(device: torch.device, T: int, e_local: int, hidden: int, inter: int) -> Workspace:
+    key = (device.type, device.index, e_local, hidden, inter)
+    ws = _workspaces.get(key)
+    if ws is None or ws.T < T:
+        cap = max(T, 1)
+        if ws is not None:
+            cap = max(cap, 2 * ws.T if ws.T < 4096 else T)
+            del _workspaces[key]
+            del ws
+        ws = Workspace(device, cap, e_local, hidden, inter)
+        _workspaces[key] = ws
+    return ws
+
+
+def clear_workspaces() -> None:
+    _workspaces.clear()
+
+
+def _dtype_tag(t: torch.Tensor, what: str) -> int:
+    if t.dtype == torch.float32:
+        return _capi.F32
+    if t.dtype == torch.bfloat16:
+        return _capi.BF16
+    raise TypeError(f"{what} must be float32 or bfloat16, got {t.dtype}")
+
+
+def _scale_strides(scale: torch.Tensor, T: int, kblocks: int) -> Tuple[int, int]:
+    """(stride over tokens, stride over K blocks) of hidden_states_scale, in elements.
+
+    [K/128, T] is the entry point's layout; [T, K/128] is accepted too, and the square
+    case T == K/128 is read as [K/128, T] like the reference (moe_fused.cu:790-811).
+    """
+    if scale.dim() != 2:
+        raise ValueError("hidden_states_scale must be 2-D")
+    if tuple(scale.shape) == (kblocks, T):
+        return scale.stride(1), scale.stride(0)
+    if tuple(scale.shape) == (T, kblocks):
+        return scale.stride(0), scale.stride(1)
+    raise ValueError(f"hidden_states_scale has shape {tuple(scale.shape)}, expected "
+                     f"({kblocks}, {T}) or ({T}, {kblocks})")
+
+
+def _as_bytes(t: torch.Tensor, what: str) -> torch.Tensor:
+    if t.dtype == torch.float8_e4m3fn:
+        return t.view(torch.uint8)
+    if t.dtype == torch.uint8:
+        return t
+    raise TypeError(f"{what} must be float8_e4m3fn (or its uint8 bit pattern), got {t.dtype}")
+
+
+def _check_inputs(routing_logits, routing_bias, hidden_states, hidden_states_scale,
+                  gemm1_weights, gemm1_weights_scale, gemm2_weights, gemm2_weights_scale):
+    dev = hidden_states.device
+    if dev.type != "cuda":
+        raise RuntimeError("fused_moe_b200 runs on CUDA tensors only (there is no CPU path)")
+    for name, t in (("routing_logits", routing_logits), ("routing_bias", routing_bias),
+                    ("hidden_states_scale", hidden_states_scale), ("gemm1_weights", gemm1_weights),
+                    ("gemm1_weights_scale", gemm1_weights_scale), ("gemm2_weights", gemm2_weights),
+                    ("gemm2_weights_scale", gemm2_weights_scale)):
+        if t.device != dev:
+            raise RuntimeError(f"{name} is on {t.device}, hidden_states on {dev}")
+    if routing_logits.dim() != 2 or routing_logits.shape[1] != E_GLOBAL:
+        raise ValueError(f"routing_logits must be [T, {E_GLOBAL}]")
+    if routing_bias.numel() != E_GLOBAL:
+        raise ValueError(f"routing_bias must have {E_GLOBAL} elements")
+    T = routing_logits.shape[0]
+    if gemm1_weights.dim() != 3 or gemm2_weights.dim() != 3:
+        raise ValueError("gemm weights must be [E_local, N, K]")
+    e_local, n1, hidden = gemm1_weights.shape
+    inter = n1 // 2
+    if tuple(gemm2_weights.shape) != (e_local, hidden, inter):
+        raise ValueError(f"gemm2_weights must be [{e_local}, {hidden}, {inter}]")
+    if tuple(hidden_states.shape) != (T, hidden):
+        raise ValueError(f"hidden_states must be [{T}, {hidden}]")
+    if tuple(gemm1_weights_scale.shape) != (e_local, n1 // BLOCK, hidden // BLOCK):
+        raise ValueError("gemm1_weights_scale must be [E_local, 2*inter/128, hidden/128]")
+    if tuple(gemm2_weights_scale.shape) != (e_local, hidden // BLOCK, inter // BLOCK):
+        raise ValueError("gemm2_weights_scale must be [E_local, hidden/128, inter/128]")
+    for name, t in (("hidden_states_scale", hidden_states_scale),
+                    ("gemm1_weights_scale", gemm1_weights_scale),
+                    ("gemm2_weights_scale", gemm2_weights_scale)):
+        if t.dtype != torch.float32:
+            raise TypeError(f"{name} must be float32")
+    return dev, T, e_local, hidden, inter
+
+
+def custom_kernel(routing_logits, routing_bias, hidden_states, hidden_states_scale,
+                  gemm1_weights, gemm1_weights_scale, gemm2_weights, gemm2_weights_scale,
+                  local_expert_offset, routed_scaling_factor, *, out: Optional[torch.Tensor] = None,
+                  check_status: bool = False) -> torch.Tensor:
+    dev, T, e_local, hidden, inter = _check_inputs(
+        routing_logits, routing_bias, hidden_states, hidden_states_scale,
+        gemm1_weights, gemm1_weights_scale, gemm2_weights, gemm2_weights_scale)
+    local_off = int(local_expert_offset)
+    rsf = float(routed_scaling_factor)
+
+    logits = routing_logits if routing_logits.is_contiguous() else routing_logits.contiguous()
+    bias = routing_bias.reshape(-1)
+    bias = bias if bias.is_contiguous() else bias.contiguous()
+    hs = _as_bytes(hidden_states, "hidden_states")
+    if hs.stride(1) != 1 or hs.stride(0) % 16 != 0:
+        hs = hs.contiguous()
+    w1 = _as_bytes(gemm1_weights, "gemm1_weights")
+    w2 = _as_bytes(gemm2_weights, "gemm2_weights")
+    s1, s2 = gemm1_weights_scale, gemm2_weights_scale
+    if not (w1.is_contiguous() and w2.is_contiguous() and s1.is_contiguous() and s2.is_contiguous()):
+        raise ValueError("expert weights and their scales must be contiguous")
+    st_t, st_kb = _scale_strides(hidden_states_scale, T, hidden // BLOCK)
+
+    with torch.cuda.device(dev):
+        ws = get_workspace(dev, T, e_local, hidden, inter)
+        if out is None:
+            result = ws.out[:T]
+        else:
+            if out.dtype != torch.bfloat16 or tuple(out.shape) != (T, hidden) or out.stride(1) != 1:
+                raise ValueError(f"out must be bfloat16 [{T}, {hidden}] with unit inner stride")
+            result = out
+        if T == 0:
+            return result
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        rc = _capi.lib().b200moe_run(
+            logits.data_ptr(), _dtype_tag(logits, "routing_logits"),
+            bias.data_ptr(), _dtype_tag(bias, "routing_bias"),
+            hs.data_ptr(), hs.stride(0),
+            hidden_states_scale.data_ptr(), st_t, st_kb,
+            w1.data_ptr(), s1.data_ptr(), w2.data_ptr(), s2.data_ptr(),
+            T, e_local, local_off, rsf, hidden, inter,
+            ws.ptr, ws.nbytes, result.data_ptr(), result.stride(0), stream)
+        _capi.check(rc, "b200moe_run")
+        if check_status:
+            code, detail = ws.read_status(stream)
+            if code != 0:
+                raise MoEError(code, "device status after b200moe_run", f"detail={detail}")
+    return result
+
+
+def kernel(*args, **kwargs):
+    return custom_kernel(*args, **kwargs)
+
+
+def run(routing_logits, routing_bias, hidden_states, hidden_states_scale,
+        gemm1_weights, gemm1_weights_scale, gemm2_weights, gemm2_weights_scale,
+        local_expert_offset, routed_scaling_factor):
+    """The reference's entry point (solution/python/kernel.py:642-648), same ten arguments."""
+    return custom_kernel(routing_logits, routing_bias, hidden_states, hidden_states_scale,
+                         gemm1_weights, gemm1_weights_scale, gemm2_weights, gemm2_weights_scale,
+                         local_expert_offset, routed_scaling_factor)
+
+
+def route(routing_logits: torch.Tensor, routing_bias: torch.Tensor, routed_scaling_factor: float,
+          local_expert_offset: int = 0, e_local: int = 32, hidden: int = 7168, inter: int = 2048):
+    """Routing alone: (ids int32 [T,8], weights fp32 [T,8]); the histogram stays in the workspace."""
+    dev = routing_logits.device
+    T = routing_logits.shape[0]
+    logits = routing_logits.contiguous()
+    bias = routing_bias.reshape(-1).contiguous()
+    ids = torch.empty((T, TOP_K), dtype=torch.int32, device=dev)
+    w = torch.empty((T, TOP_K), dtype=torch.float32, device=dev)
+    if T == 0:
+        return ids, w
+    with torch.cuda.device(dev):
+        ws = get_workspace(dev, T, e_local, hidden, inter)
+        rc = _capi.lib().b200moe_route(
+            logits.data_ptr(), _dtype_tag(logits, "routing_logits"), bias.data_ptr(),
+            _dtype_tag(bias, "routing_bias"), T, float(routed_scaling_factor), int(local_expert_offset),
+            e_local, hidden, inter, ids.data_ptr(), w.data_ptr(), ws.ptr, ws.nbytes,
+            torch.cuda.current_stream(dev).cuda_stream)
+        _capi.check(rc, "b200moe_route")
+    return ids, w
+
+
+def launches_per_run(T: int, e_local: int) -> int:
+    return int(_capi.lib().b200moe_launches_per_run(T, e_local))
