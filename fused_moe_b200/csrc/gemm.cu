@@ -134,12 +134,19 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       constexpr uint32_t idesc = make_idesc_e4m3(kTileM, BN);
       uint32_t it = 0;
       bool alive = true;
+      long long mma_wait_tempty = 0, mma_wait_full = 0;
       for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x) {
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const uint32_t s = it % S, ph = (it / S) & 1u;
           const uint32_t b = it & 1u, bph = (it >> 1) & 1u;
+          const long long m0 = clock64();
           if (!mbar_wait(bar_tempty + 8 * b, bph ^ 1u, abort_flag, p.status, 2)) { alive = false; break; }
+          const long long m1 = clock64();
           if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 3)) { alive = false; break; }
+          if (p.prof && blockIdx.x == 0) {
+            mma_wait_tempty += m1 - m0;
+            mma_wait_full += clock64() - m1;
+          }
           tc_fence_after();
           const uint32_t a_addr = smem_base + s * Cfg::kStageBytes;
           const uint32_t b_addr = a_addr + kABytes;
@@ -156,6 +163,10 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       // All MMAs must retire before TMEM is freed.
       tc_commit(bar_drain);
       (void)mbar_wait(bar_drain, 0u, abort_flag + 1, p.status, 5);
+      if (p.prof && blockIdx.x == 0) {
+        p.prof[7] = (unsigned long long)mma_wait_tempty;   // MMA thread waiting for the epilogue
+        p.prof[8] = (unsigned long long)mma_wait_full;     // MMA thread waiting for TMA data
+      }
     }
   } else {
     // ------------------------------ promotion + epilogue ------------------------------
@@ -166,7 +177,11 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     constexpr int CH = Cfg::kChunks;
     uint32_t it = 0;
     bool alive = true;
+    const bool prof_me = p.prof && blockIdx.x == 0 && warp == 2 && lane == 0;
+    const long long t_begin = clock64();
+    long long t_tile_epi = 0, t_tile_head = 0;
     for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x) {
+      const long long th0 = clock64();
       const int m_tile = w / p.n_tiles, n_tile = w % p.n_tiles;
       const int e = p.tile_expert[m_tile];
       const int row = m_tile * kTileM + q * 32 + lane;
@@ -192,6 +207,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       float sa_n = MODE == 1 ? sa_ptr[0] : 1.f;
       float sb0_n = sb0_ptr[0];
       float sb1_n = MODE == 1 ? sb1_ptr[0] : 0.f;
+      t_tile_head += clock64() - th0;
 
       for (int kb = 0; kb < kblocks; ++kb, ++it) {
         const uint32_t b = it & 1u, bph = (it >> 1) & 1u;
@@ -204,10 +220,13 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           }
           sb0_n = sb0_ptr[kb + 1];
         }
+        long long c0 = clock64();
         bool ok = mbar_wait(bar_tfull + 8 * b, bph, abort_flag, p.status, 4);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { alive = false; break; }
         tc_fence_after();
+        long long c1 = clock64();
+        long long ld_cycles = 0;
         const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + b * BN;
 #pragma unroll
         for (int c = 0; c < CH; ++c) {
@@ -222,16 +241,26 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             sc = sc0;
           }
           uint32_t r[32];
+          long long l0 = clock64();
           tmem_ld_32x32(t_row + col, r);
           tmem_ld_wait();
+          ld_cycles += clock64() - l0;
 #pragma unroll
           for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(__uint_as_float(r[j]), sc, acc[c * 32 + j]);
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
+        if (p.prof && blockIdx.x == 0 && warp == 2 && lane == 0) {
+          long long c2 = clock64();
+          atomicAdd((unsigned long long*)p.prof + 0, (unsigned long long)(c1 - c0));   // wait for accumulator
+          atomicAdd((unsigned long long*)p.prof + 1, (unsigned long long)(c2 - c1));   // promotion
+          atomicAdd((unsigned long long*)p.prof + 2, (unsigned long long)ld_cycles);   // of which tcgen05.ld + wait
+          atomicAdd((unsigned long long*)p.prof + 3, 1ull);                            // K blocks
+        }
       }
       if (!alive) break;
+      const long long te0 = clock64();
 
       if (tok >= 0) {
         if (MODE == 1) {
@@ -258,6 +287,12 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
             red_add_v4(dst + j, acc[j] * rs, acc[j + 1] * rs, acc[j + 2] * rs, acc[j + 3] * rs);
         }
       }
+      t_tile_epi += clock64() - te0;
+    }
+    if (prof_me) {
+      p.prof[4] = (unsigned long long)(clock64() - t_begin);   // whole role
+      p.prof[5] = (unsigned long long)t_tile_epi;              // per-tile epilogues
+      p.prof[6] = (unsigned long long)t_tile_head;             // per-tile set-up loads
     }
   }
 

@@ -39,6 +39,7 @@ struct GemmParams {
   const float* row_weight;  // GEMM2 in: routing weight per row
   float* out_acc;           // GEMM2 out: [T][hidden] fp32, accumulated with red.add
   int* status;
+  unsigned long long* prof;   // optional cycle counters of CTA 0 (null: off)
 };
 
 // mode 1: GEMM1 + SwiGLU + row amax; mode 2: GEMM2 + weighted combine.  bn: 128 or 256.

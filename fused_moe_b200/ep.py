@@ -75,6 +75,7 @@ class CudaOps:
         w1b, w2b = _k._as_bytes(w1, "gemm1_weights"), _k._as_bytes(w2, "gemm2_weights")
         with torch.cuda.device(dev):
             ws = _k.get_workspace(dev, n_rows, e_local, hidden, inter)
+            ws.last_T = n_rows
             stream = torch.cuda.current_stream(dev).cuda_stream
             ids_ptr = base + hidden + 4 * kb
             rc = _capi.lib().b200moe_count(ids_ptr, rb // 4, n_rows, local_off, e_local, hidden, inter,

@@ -41,7 +41,8 @@ class Workspace:
 
     def __init__(self, device: torch.device, T: int, e_local: int, hidden: int, inter: int):
         self.device, self.T, self.e_local, self.hidden, self.inter = device, T, e_local, hidden, inter
-        self.layout = _capi.workspace_layout(T, e_local, hidden, inter)
+        self.layout = _capi.workspace_layout(T, e_local, hidden, inter)   # carve-up at full capacity
+        self.last_T = T            # token count of the last call: the library carves for that count
         self.nbytes = int(self.layout.total_bytes)
         # zero-filled once so that padding rows never hold NaN bit patterns from a previous owner
         self.buffer = torch.zeros(self.nbytes + 256, dtype=torch.uint8, device=device)
@@ -49,9 +50,14 @@ class Workspace:
         self._skip = self.ptr - self.buffer.data_ptr()
         self.out = torch.empty((max(T, 1), hidden), dtype=torch.bfloat16, device=device)
 
+    def layout_of_last_call(self):
+        """Offsets as the library computed them for the last call's token count (they depend
+        on it, not on the capacity of this buffer)."""
+        return _capi.workspace_layout(self.last_T, self.e_local, self.hidden, self.inter)
+
     def view(self, name: str, dtype: torch.dtype, shape) -> torch.Tensor:
-        """A typed view of one intermediate (tests and tools)."""
-        off = int(getattr(self.layout, name)) + self._skip
+        """A typed view of one intermediate of the last call (tests and tools)."""
+        off = int(getattr(self.layout_of_last_call(), name)) + self._skip
         n = 1
         for s in shape:
             n *= int(s)
@@ -187,6 +193,7 @@ def custom_kernel(routing_logits, routing_bias, hidden_states, hidden_states_sca
         if T == 0:
             return result
         stream = torch.cuda.current_stream(dev).cuda_stream
+        ws.last_T = T
         rc = _capi.lib().b200moe_run(
             logits.data_ptr(), _dtype_tag(logits, "routing_logits"),
             bias.data_ptr(), _dtype_tag(bias, "routing_bias"),
@@ -229,6 +236,7 @@ def route(routing_logits: torch.Tensor, routing_bias: torch.Tensor, routed_scali
         return ids, w
     with torch.cuda.device(dev):
         ws = get_workspace(dev, T, e_local, hidden, inter)
+        ws.last_T = T
         rc = _capi.lib().b200moe_route(
             logits.data_ptr(), _dtype_tag(logits, "routing_logits"), bias.data_ptr(),
             _dtype_tag(bias, "routing_bias"), T, float(routed_scaling_factor), int(local_expert_offset),

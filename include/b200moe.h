@@ -154,6 +154,12 @@ B200MOE_API int b200moe_run(const void* logits, int logits_dtype, const void* bi
  * code a kernel recorded; `detail` (host, may be NULL) receives int32[4] of context. */
 B200MOE_API int b200moe_read_status(const void* workspace, void* stream, int32_t* detail /* host */);
 
+/* Measurement hook (no counterpart in the reference, whose per-stage timing replays the
+ * pipeline stage by stage from Python, experiments/fast_bench/bench_server.py:470-632):
+ * the calling thread's next b200moe_experts / b200moe_run records `start_event` before and
+ * `stop_event` after its GEMM1 launch (cudaEvent_t as void*, either may be NULL), once. */
+B200MOE_API int b200moe_profile_next_gemm1(void* start_event, void* stop_event);
+
 /* Number of kernels b200moe_run launches for this problem (memsets not counted). */
 B200MOE_API int b200moe_launches_per_run(int T, int e_local);
 

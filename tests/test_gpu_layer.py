@@ -1,0 +1,147 @@
+"""GPU parity of the whole layer through the C ABI (via the host entry point)."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN, golden_inputs, load_golden
+from fused_moe_b200 import kernel as K
+from fused_moe_b200 import synth
+from oracle import moe_oracle as O
+import gpu_checks
+
+pytestmark = pytest.mark.gpu
+
+SMALL = sorted(os.path.basename(p)[:-4] for p in glob.glob(os.path.join(GOLDEN, "layer_small_*.npz")))
+
+
+def _golden_out(g):
+    return torch.from_numpy(g["out_bits"].view(np.int16).copy()).view(torch.bfloat16)
+
+
+@pytest.mark.parametrize("name", SMALL)
+def test_small_shapes_match_reference_vectors_stage_by_stage(name):
+    g, inp = golden_inputs(name)
+    res, ws = gpu_checks.run_gpu(inp)
+    info = gpu_checks.check_stages(inp, res, ws, verbose=True)
+    # and against the stored output of the reference's own function
+    ids = ws.view("topk_ids", torch.int32, (g["ids"].shape[0], 8)).cpu().numpy()
+    assert np.array_equal(ids.astype(np.uint8), g["ids"])
+    frac_all, frac_nz, max_abs = synth.check_close(res, _golden_out(g))
+    assert frac_all >= 0.999 and frac_nz >= 0.999, (frac_all, frac_nz, max_abs, info)
+
+
+@pytest.mark.parametrize("name", ["layer_full_T8_ts0", "layer_full_T8_ts1", "layer_full_T8_ts2",
+                                  "layer_full_T1_ts1", "layer_full_T64_ts0"])
+def test_benchmark_shape_matches_reference_vectors(name, full_weights_cpu, full_weights_gpu):
+    g, inp = golden_inputs(name, weights=full_weights_cpu)
+    dev = torch.device("cuda", 0)
+    gi = synth.MoEInputs(inp.routing_logits.to(dev), inp.routing_bias.to(dev), inp.hidden_states.to(dev),
+                         inp.hidden_states_scale.to(dev), *full_weights_gpu, inp.local_expert_offset,
+                         inp.routed_scaling_factor)
+    res = K.custom_kernel(*gi.args(), check_status=True)
+    T = g["ids"].shape[0]
+    ws = K.get_workspace(dev, T, 32, synth.HIDDEN, synth.INTER)
+    ids = ws.view("topk_ids", torch.int32, (T, 8)).cpu().numpy()
+    assert np.array_equal(ids.astype(np.uint8), g["ids"]), "expert ids must be bit-exact"
+    w = ws.view("topk_w", torch.float32, (T, 8)).cpu().numpy()
+    np.testing.assert_allclose(w, g["weights"], rtol=1e-6, atol=0)
+    frac_all, frac_nz, max_abs = synth.check_close(res, _golden_out(g))
+    # tolerance of the benchmark definition: |out-ref| <= 0.05 + 0.05|ref| on >= 99.9 %
+    assert frac_all >= 0.999 and frac_nz >= 0.999, (name, frac_all, frac_nz, max_abs)
+
+
+@pytest.mark.parametrize("T,tseed,zipf", [(4, 1, False), (16, 0, False), (1024, 0, False), (2048, 0, True)])
+def test_benchmark_shape_against_oracle(T, tseed, zipf, full_weights_cpu, full_weights_gpu):
+    """Decode, prefill and the Zipf load-imbalance stress at the full shape (oracle computed here)."""
+    inp = synth.make_inputs(T=T, seed=0, token_seed=tseed, zipf=zipf, weights=full_weights_cpu)
+    dev = torch.device("cuda", 0)
+    gi = synth.MoEInputs(inp.routing_logits.to(dev), inp.routing_bias.to(dev), inp.hidden_states.to(dev),
+                         inp.hidden_states_scale.to(dev), *full_weights_gpu, 0, 2.5)
+    res = K.custom_kernel(*gi.args(), check_status=True)
+    ora = O.moe_layer_torch(*inp.args())
+    ws = K.get_workspace(dev, T, 32, synth.HIDDEN, synth.INTER)
+    ids = ws.view("topk_ids", torch.int32, (T, 8)).cpu().numpy()
+    assert np.array_equal(ids, ora["ids"]), "expert ids must be bit-exact"
+    counts = ws.view("expert_count", torch.int32, (32,)).cpu().numpy()
+    assert np.array_equal(counts, O.local_counts(ora["ids"], 0, 32))
+    if zipf:
+        assert (counts == 0).sum() >= 16 and counts.max() >= T - 1, "Zipf bias should starve most experts"
+    frac_all, frac_nz, max_abs = synth.check_close(res, ora["out"])
+    assert frac_all >= 0.999 and frac_nz >= 0.999, (T, frac_all, frac_nz, max_abs)
+
+
+def test_run_twice_is_bit_identical_up_to_reduction_order_and_out_argument():
+    g, inp = golden_inputs("layer_small_T200_off64")
+    dev = torch.device("cuda", 0)
+    gi = inp.to(dev)
+    a = K.run(*gi.args()).clone()
+    b = K.run(*gi.args()).clone()
+    # fp32 reductions into the output may land in a different order; everything before them is deterministic
+    assert (a.float() - b.float()).abs().max().item() <= 2 ** -6
+    own = torch.empty_like(a)
+    r = K.custom_kernel(*gi.args(), out=own)
+    assert r.data_ptr() == own.data_ptr()
+    assert (own.float() - a.float()).abs().max().item() <= 2 ** -6
+
+
+def test_scale_layouts_and_bf16_logits():
+    g, inp = golden_inputs("layer_small_T64_off0")
+    dev = torch.device("cuda", 0)
+    gi = inp.to(dev)
+    base = K.run(*gi.args()).clone()
+    args = list(gi.args())
+    args[3] = gi.hidden_states_scale.t().contiguous()            # [T, K/128]
+    alt = K.run(*args).clone()
+    assert torch.equal(base, alt) or (base.float() - alt.float()).abs().max().item() <= 2 ** -6
+    args = list(gi.args())
+    args[3] = gi.hidden_states_scale.t().contiguous().t()        # [K/128, T] view with swapped strides
+    alt = K.run(*args).clone()
+    assert (base.float() - alt.float()).abs().max().item() <= 2 ** -6
+    # bf16 logits are accepted (the reference's harness passes them); compare with the oracle on the same values
+    args = list(gi.args())
+    args[0] = gi.routing_logits.to(torch.bfloat16)
+    res = K.run(*args).clone()
+    cpu_args = list(inp.args())
+    cpu_args[0] = inp.routing_logits.to(torch.bfloat16).float()
+    ora = O.moe_layer_torch(*cpu_args)
+    assert synth.check_close(res, ora["out"])[0] >= 0.999
+
+
+def test_empty_batch_and_errors():
+    g, inp = golden_inputs("layer_small_T64_off0")
+    dev = torch.device("cuda", 0)
+    gi = inp.to(dev)
+    args = list(gi.args())
+    args[0] = args[0][:0]
+    args[2] = args[2][:0]
+    args[3] = args[3][:, :0]
+    out = K.run(*args)
+    assert out.shape == (0, 512)
+    bad = list(gi.args())
+    bad[4] = bad[4][:, :, :384]                                   # hidden not a multiple of 256
+    with pytest.raises((ValueError, K.MoEError)):
+        K.run(*bad)
+    bad = list(gi.args())
+    bad[8] = 250                                                  # experts 250..281 do not exist
+    with pytest.raises(K.MoEError):
+        K.run(*bad)
+
+
+def test_routing_ids_bit_exact_on_every_benchmark_token_count():
+    g = load_golden("routing_ids")
+    dev = torch.device("cuda", 0)
+    for key in sorted(k[:-4] for k in g.files if k.endswith("_ids")):
+        parts = key.split("_")
+        T = int(parts[0][1:])
+        zipf = "zipf" in key
+        seed = 1 if key.endswith("_s1") else 0
+        rank = int(parts[1][4:]) if parts[1].startswith("rank") else 0
+        logits, _, _ = synth.make_tokens(T, rank, seed, hidden=128)
+        bias = synth.make_bias(seed, zipf)
+        ids, w = K.route(logits.to(dev), bias.to(dev), 2.5, 0, 32, 256, 128)
+        assert np.array_equal(ids.cpu().numpy().astype(np.uint8), g[key + "_ids"]), f"{key}: ids differ"
+        if key + "_w" in g.files:
+            np.testing.assert_allclose(w.cpu().numpy(), g[key + "_w"], rtol=1e-6, atol=0)
