@@ -3,7 +3,7 @@
 //
 // Launch sequence of b200moe_run (all on the caller's stream, nothing allocated):
 //   memset counters | route (+histogram) | scan | place | gather | GEMM1(+SwiGLU,+row max)
-//   | requant | GEMM2(+weighted combine) | finalize(bf16)
+//   | requant | GEMM2(+row scale * routing weight, bf16 rows) | combine (per-token sum)
 // It replaces the two Python pipelines of the reference
 // (solution/python/kernel.py:381-429 and 432-572), which need a host synchronisation
 // above 2048 tokens (kernel.py:196); here tile counts stay on the device.
@@ -135,9 +135,11 @@ void compute_layout(int T, int e_local, int hidden, int inter, b200moe_ws_layout
   L->row_amax = take((uint64_t)m_cap * 4);
   L->act_q = take((uint64_t)m_cap * inter);
   L->row_scale = take((uint64_t)m_cap * 4);
-  L->out_acc = take((uint64_t)(T > 0 ? T : 1) * hidden * 4);
+  L->y = take((uint64_t)m_cap * hidden * 2);
+  L->tok_rows = take((uint64_t)(T > 0 ? T : 1) * kTopK * 4);
   L->topk_ids = take((uint64_t)(T > 0 ? T : 1) * kTopK * 4);
   L->topk_w = take((uint64_t)(T > 0 ? T : 1) * kTopK * 4);
+  L->trace = take(2 * 4 * 64 * 8);   // B200MOE_PROF: absolute cycle stamps of CTA 0's first 64 K blocks
   L->total_bytes = off;
 }
 
@@ -198,7 +200,7 @@ int b200moe_profile_next_gemm1(void* start_event, void* stop_event) {
 
 int b200moe_launches_per_run(int T, int e_local) {
   (void)e_local;
-  return T > 0 ? 8 : 0;   // route, scan, place, gather, gemm1, requant, gemm2, finalize
+  return T > 0 ? 8 : 0;   // route, scan, place, gather, gemm1, requant, gemm2, combine
 }
 
 int b200moe_route(const void* logits, int logits_dtype, const void* bias, int bias_dtype, int T,
@@ -252,17 +254,13 @@ int b200moe_experts(const int32_t* topk_ids, int64_t ids_row_stride, const float
   if (rc != B200MOE_OK) return rc;
   if (hidden_row_stride < hidden || hidden_row_stride % 16 != 0 ||
       reinterpret_cast<uintptr_t>(hidden_states) % 16 != 0 || reinterpret_cast<uintptr_t>(w1) % 16 != 0 ||
-      reinterpret_cast<uintptr_t>(w2) % 16 != 0 || reinterpret_cast<uintptr_t>(out_bf16) % 8 != 0 ||
-      out_row_stride < hidden || out_row_stride % 4 != 0)
+      reinterpret_cast<uintptr_t>(w2) % 16 != 0 || reinterpret_cast<uintptr_t>(out_bf16) % 16 != 0 ||
+      out_row_stride < hidden || out_row_stride % 8 != 0)
     return B200MOE_ERR_MISALIGNED;
   if (T == 0) return B200MOE_OK;
   int num_sms = 0;
   if ((rc = ensure_device(&num_sms)) != B200MOE_OK) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-
-  // scratch that accumulates: row maxima and the fp32 output
-  CUDA_TRY(cudaMemsetAsync(ws.base + ws.L.row_amax, 0, (size_t)ws.L.m_cap * 4, st));
-  CUDA_TRY(cudaMemsetAsync(ws.base + ws.L.out_acc, 0, (size_t)T * hidden * 4, st));
 
   CUDA_TRY(launch_permute(ws, topk_ids, ids_row_stride, topk_w, w_row_stride, hidden_states, hidden_row_stride,
                           hidden_scale, scale_stride_t, scale_stride_kb, T, e_local, local_expert_offset, hidden,
@@ -297,6 +295,7 @@ int b200moe_experts(const int32_t* topk_ids, int64_t ids_row_stride, const float
   // (GEMM1: 9 x u64 at meta+32, GEMM2: at meta+136); cleared with the counters each call.
   static const bool prof_on = getenv("B200MOE_PROF") != nullptr;
   g1.prof = prof_on ? ws.at<unsigned long long>(ws.L.meta + 32) : nullptr;
+  g1.trace = prof_on ? ws.at<unsigned long long>(ws.L.trace) : nullptr;
   if (g_prof_start) CUDA_TRY(cudaEventRecord(g_prof_start, st));
   CUDA_TRY(launch_grouped_gemm(1, bn, g1, num_sms, st));
   if (g_prof_stop) CUDA_TRY(cudaEventRecord(g_prof_stop, st));
@@ -324,12 +323,13 @@ int b200moe_experts(const int32_t* topk_ids, int64_t ids_row_stride, const float
   g2.hidden = hidden;
   g2.row_scale = ws.at<float>(ws.L.row_scale);
   g2.row_weight = ws.at<float>(ws.L.row_weight);
-  g2.out_acc = ws.at<float>(ws.L.out_acc);
+  g2.y = ws.at<__nv_bfloat16>(ws.L.y);
   g2.status = g1.status;
   g2.prof = prof_on ? ws.at<unsigned long long>(ws.L.meta + 136) : nullptr;
+  g2.trace = prof_on ? ws.at<unsigned long long>(ws.L.trace) + 4 * 64 : nullptr;
   CUDA_TRY(launch_grouped_gemm(2, bn, g2, num_sms, st));
 
-  CUDA_TRY(launch_finalize(ws.at<float>(ws.L.out_acc), T, hidden, out_bf16, out_row_stride, num_sms, st));
+  CUDA_TRY(launch_combine(ws, T, hidden, out_bf16, out_row_stride, num_sms, st));
   return B200MOE_OK;
 }
 

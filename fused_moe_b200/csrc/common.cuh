@@ -184,6 +184,35 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// tcgen05.wait::ld that also names the loaded registers as read-write operands, so that no
+// use of them can be scheduled ahead of the wait by the compiler.
+#define B200MOE_RW8(r, o) "+r"(r[o]), "+r"(r[o + 1]), "+r"(r[o + 2]), "+r"(r[o + 3]), "+r"(r[o + 4]), "+r"(r[o + 5]), "+r"(r[o + 6]), "+r"(r[o + 7])
+__device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&a)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : B200MOE_RW8(a, 0), B200MOE_RW8(a, 8), B200MOE_RW8(a, 16), B200MOE_RW8(a, 24)
+               :
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait_on(uint32_t (&a)[32], uint32_t (&b)[32]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;"
+               : B200MOE_RW8(a, 0), B200MOE_RW8(a, 8), B200MOE_RW8(a, 16), B200MOE_RW8(a, 24),
+                 B200MOE_RW8(b, 0), B200MOE_RW8(b, 8), B200MOE_RW8(b, 16), B200MOE_RW8(b, 24)
+               :
+               : "memory");
+}
+
+// Register budget moves between warpgroups (all four warps of a warpgroup must execute it).
+template <int N> __device__ __forceinline__ void reg_alloc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N> __device__ __forceinline__ void reg_dealloc() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }

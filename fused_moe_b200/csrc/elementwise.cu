@@ -1,11 +1,12 @@
-// Row-wise e4m3 requantisation of the SwiGLU output and the bf16 finalisation of the output.
+// Row-wise e4m3 requantisation of the SwiGLU output and the per-token combine of the output.
 //
 // requant replaces the back half of the reference's `swiglu_fp8_requant_kernel`
 // (solution/python/moe_fused.cu:175-195): one scale per row, scale = max(amax/448, 1e-8),
 // values rounded to nearest even.  The row maximum comes from GEMM1's epilogue, so the
 // fp32 activations are read exactly once here.
-// finalize replaces the bf16 write of `reduce_scatter_from_2d_perm_kernel`
-// (moe_fused.cu:346-393): the fp32 sums of GEMM2's epilogue are rounded once to bf16.
+// combine replaces `reduce_scatter_from_2d_perm_kernel` / `weighted_scatter_kernel`
+// (moe_fused.cu:346-393, 490-517): a gather per token over its rows instead of atomics,
+// so the output is bit-reproducible.
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -44,19 +45,53 @@ requant_kernel(Workspace ws, int inter) {
   }
 }
 
+// out[t,:] = sum of the token's rows, taken in ascending packed-row order (= ascending
+// expert) and rounded to bf16 after every addition: the arithmetic of the reference's
+// `out[t] += bf16(G2 * w)` loop (experiments/fast_bench/correctness_bench.py:107-111).
 __global__ void __launch_bounds__(256)
-finalize_kernel(const float* __restrict__ acc, int T, int hidden, __nv_bfloat16* __restrict__ out, long long stride) {
-  const int vec_per_row = hidden / 4;
+combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ tok_rows, int T, int hidden,
+               __nv_bfloat16* __restrict__ out, long long stride) {
+  const int vec_per_row = hidden / 8;   // 8 bf16 = 16 bytes
   const long long n = (long long)T * vec_per_row;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-    int t = (int)(i / vec_per_row), v = (int)(i % vec_per_row);
-    float4 x = reinterpret_cast<const float4*>(acc)[i];
-    __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y);
-    __nv_bfloat162 hi = __floats2bfloat162_rn(x.z, x.w);
-    uint2 pk;
-    pk.x = *reinterpret_cast<uint32_t*>(&lo);
-    pk.y = *reinterpret_cast<uint32_t*>(&hi);
-    *reinterpret_cast<uint2*>(out + (size_t)t * stride + 4 * v) = pk;
+    const int t = (int)(i / vec_per_row), v = (int)(i % vec_per_row);
+    int rows[kTopK];
+    {
+      const int4 a = reinterpret_cast<const int4*>(tok_rows + (size_t)t * kTopK)[0];
+      const int4 b = reinterpret_cast<const int4*>(tok_rows + (size_t)t * kTopK)[1];
+      rows[0] = a.x; rows[1] = a.y; rows[2] = a.z; rows[3] = a.w;
+      rows[4] = b.x; rows[5] = b.y; rows[6] = b.z; rows[7] = b.w;
+    }
+    // ascending order with -1 (not local) last: 8-element insertion sort on keys
+#pragma unroll
+    for (int a = 1; a < kTopK; ++a) {
+#pragma unroll
+      for (int b = a; b > 0; --b) {
+        unsigned x = (unsigned)rows[b - 1], z = (unsigned)rows[b];
+        if (z < x) { rows[b - 1] = (int)z; rows[b] = (int)x; }
+      }
+    }
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+    for (int k = 0; k < kTopK; ++k) {
+      if (rows[k] < 0) break;
+      const uint4 raw = reinterpret_cast<const uint4*>(y + (size_t)rows[k] * hidden)[v];
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(p2[j]);
+        // bf16 + bf16 in fp32 is exact before the rounding, so this equals a bf16 addition
+        acc[2 * j] = __bfloat162float(__float2bfloat16_rn(acc[2 * j] + f.x));
+        acc[2 * j + 1] = __bfloat162float(__float2bfloat16_rn(acc[2 * j + 1] + f.y));
+      }
+    }
+    uint4 pk;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    *reinterpret_cast<uint4*>(out + (size_t)t * stride + 8 * v) = pk;
   }
 }
 
@@ -71,15 +106,15 @@ cudaError_t launch_requant(const Workspace& ws, int inter, int num_sms, cudaStre
   return cudaGetLastError();
 }
 
-cudaError_t launch_finalize(const float* out_acc, int T, int hidden, void* out_bf16, long long out_row_stride,
-                            int num_sms, cudaStream_t stream) {
+cudaError_t launch_combine(const Workspace& ws, int T, int hidden, void* out_bf16, long long out_row_stride,
+                           int num_sms, cudaStream_t stream) {
   if (T <= 0) return cudaSuccess;
-  long long n = (long long)T * (hidden / 4);
+  long long n = (long long)T * (hidden / 8);
   int blocks = (int)((n + 255) / 256);
   int cap = num_sms * 16;
   if (blocks > cap) blocks = cap;
-  finalize_kernel<<<blocks, 256, 0, stream>>>(out_acc, T, hidden, reinterpret_cast<__nv_bfloat16*>(out_bf16),
-                                              out_row_stride);
+  combine_kernel<<<blocks, 256, 0, stream>>>(ws.at<__nv_bfloat16>(ws.L.y), ws.at<int>(ws.L.tok_rows), T, hidden,
+                                             reinterpret_cast<__nv_bfloat16*>(out_bf16), out_row_stride);
   return cudaGetLastError();
 }
 

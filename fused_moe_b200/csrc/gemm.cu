@@ -1,23 +1,24 @@
 // Persistent grouped FP8 GEMMs on tcgen05 tensor cores with exact fp32 block scales.
 //
 // Replaces the reference's CUTLASS grouped GEMM `moe_blockwise_grouped_mm_v2`
-// (solution/python/moe_gemm.cu:310-340, 418-654) plus, in the epilogues, its
-// `swiglu_fp8_requant_kernel` front half (solution/python/moe_fused.cu:131-196) and its
-// combine kernels (`weighted_scatter_kernel` moe_fused.cu:490-517,
-// `reduce_scatter_from_2d_perm_kernel` moe_fused.cu:346-393).
+// (solution/python/moe_gemm.cu:310-340, 418-654) plus, in the epilogues, the front half
+// of its `swiglu_fp8_requant_kernel` (solution/python/moe_fused.cu:131-196) and the
+// per-row scaling of its combine kernels (moe_fused.cu:346-393, 490-517).
 //
 // One CTA per SM walks work items (M tile of 128 packed rows, N tile of BN weight rows).
 // Per 128-wide K block (= one fp32 scale block, = one 128-byte swizzled TMA row):
-//   warp 0     TMA producer: A box 128x128 B and two B boxes (BN/2)x128 B into a smem ring
-//   warp 1     issues 4 tcgen05.mma (K=32 each) into one of two TMEM accumulators, starting
-//              from zero, so each accumulator holds the raw e4m3 dot product of one K block
-//   warps 2-9  read that accumulator back (tcgen05.ld) and fold it into fp32 registers as
-//              acc += (a_scale * b_scale) * partial  -- the block scales are arbitrary fp32
-//              numbers, so they cannot ride on the MMA itself
+//   warp 0      TMA producer: A box 128x128 B and two B boxes (BN/2)x128 B into a smem ring
+//   warp 1      issues 4 tcgen05.mma (K=32 each) into one of two TMEM accumulators, starting
+//               from zero, so each accumulator holds the raw e4m3 dot product of one K block
+//   warps 4-11  read that accumulator back (tcgen05.ld, two loads in flight) and fold it into
+//               fp32 registers with packed FMAs: acc += (a_scale * b_scale) * partial.  The
+//               block scales are arbitrary fp32 numbers, so they cannot ride on the MMA.
+// The control warpgroup (warps 0-3) gives registers back (setmaxnreg) so that the eight
+// promotion warps can hold a 128x256 fp32 tile (128 accumulators per thread) without spills.
 // GEMM1 pairs gate rows [n, n+BN/2) with up rows [inter+n, ...) in one tile, so the epilogue
 // computes g*silu(u) in registers, stores fp32 activations and the row maximum.
-// GEMM2's epilogue multiplies by (row requant scale * routing weight) and adds the row into
-// the token's fp32 output with vector reductions.
+// GEMM2's epilogue multiplies by (row requant scale * routing weight) and stores the row as
+// bf16; the combine kernel sums a token's rows.
 //
 // Every wait is bounded (see mbar_wait); on a timeout the CTA drains and frees its TMEM.
 #include "common.cuh"
@@ -27,9 +28,13 @@ namespace b200moe {
 
 namespace {
 
-constexpr int kGemmThreads = 320;
+constexpr int kCtrlWarps = 4;
 constexpr int kEpiWarps = 8;
+constexpr int kGemmThreads = 32 * (kCtrlWarps + kEpiWarps);   // 384: three warpgroups
+constexpr int kCtrlRegs = 56;
+constexpr int kEpiRegs = 224;   // 128*56 + 256*224 = 64512 = 384 threads * 168 registers at launch
 constexpr int kABytes = kTileM * kBlockK;   // 16 KiB
+constexpr int kScalePrefetchDist = 6;       // K blocks ahead for the activation-scale L2 prefetch
 
 template <int BN> struct TileCfg {
   static constexpr int kBBytes = BN * kBlockK;
@@ -47,7 +52,26 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   return g * (u * sig);
 }
 
+// acc[16 pairs] += scale * r[32] with packed fp32 FMAs
+__device__ __forceinline__ void fma_chunk(float2* acc, const uint32_t (&r)[32], float sc) {
+  const float2 s2 = make_float2(sc, sc);
+#pragma unroll
+  for (int j = 0; j < 16; ++j)
+    acc[j] = __ffma2_rn(make_float2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])), s2, acc[j]);
+}
+
+// First TMEM column (inside the tile) and scale selector of chunk c of a thread in column half h.
 template <int MODE, int BN>
+__device__ __forceinline__ uint32_t chunk_col(int c, int h) {
+  constexpr int CH = TileCfg<BN>::kChunks;
+  if (MODE == 1) {
+    const bool up = c >= CH / 2;
+    return (up ? BN / 2 : 0) + h * (BN / 4) + (up ? c - CH / 2 : c) * 32;
+  }
+  return h * (BN / 2) + c * 32;
+}
+
+template <int MODE, int BN, bool PROF>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   using Cfg = TileCfg<BN>;
@@ -96,9 +120,10 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   const int total_items = m_tiles * p.n_tiles;
   const int kblocks = p.kblocks;
 
-  if (warp == 0) {
-    // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
+  if (warp < kCtrlWarps) {
+    reg_dealloc<kCtrlRegs>();
+    if (warp == 0 && lane == 0) {
+      // ------------------------------ TMA producer ------------------------------
       uint32_t it = 0;
       bool alive = true;
       for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x) {
@@ -127,25 +152,27 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t first = it > (uint32_t)S ? it - S : 0u;
       for (uint32_t j = first; j < it; ++j)
         (void)mbar_wait(bar_full + 8 * (j % S), (j / S) & 1u, abort_flag + 1, p.status, 6);
-    }
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
+    } else if (warp == 1 && lane == 0) {
+      // ------------------------------ MMA issuer ------------------------------
       constexpr uint32_t idesc = make_idesc_e4m3(kTileM, BN);
       uint32_t it = 0;
       bool alive = true;
-      long long mma_wait_tempty = 0, mma_wait_full = 0;
+      long long wait_epi = 0, wait_tma = 0;
       for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x) {
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           const uint32_t s = it % S, ph = (it / S) & 1u;
           const uint32_t b = it & 1u, bph = (it >> 1) & 1u;
-          const long long m0 = clock64();
+          const long long m0 = PROF ? clock64() : 0;
           if (!mbar_wait(bar_tempty + 8 * b, bph ^ 1u, abort_flag, p.status, 2)) { alive = false; break; }
-          const long long m1 = clock64();
+          const long long m1 = PROF ? clock64() : 0;
           if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 3)) { alive = false; break; }
-          if (p.prof && blockIdx.x == 0) {
-            mma_wait_tempty += m1 - m0;
-            mma_wait_full += clock64() - m1;
+          if (PROF) {
+            wait_epi += m1 - m0;
+            wait_tma += clock64() - m1;
+            if (p.trace && blockIdx.x == 0 && it < 64) {
+              p.trace[it * 4 + 0] = (unsigned long long)m1;          // accumulator free seen by the MMA thread
+              p.trace[it * 4 + 1] = (unsigned long long)clock64();   // operands landed seen by the MMA thread
+            }
           }
           tc_fence_after();
           const uint32_t a_addr = smem_base + s * Cfg::kStageBytes;
@@ -163,43 +190,45 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       // All MMAs must retire before TMEM is freed.
       tc_commit(bar_drain);
       (void)mbar_wait(bar_drain, 0u, abort_flag + 1, p.status, 5);
-      if (p.prof && blockIdx.x == 0) {
-        p.prof[7] = (unsigned long long)mma_wait_tempty;   // MMA thread waiting for the epilogue
-        p.prof[8] = (unsigned long long)mma_wait_full;     // MMA thread waiting for TMA data
+      if (PROF && p.prof && blockIdx.x == 0) {
+        p.prof[7] = (unsigned long long)wait_epi;   // MMA thread waiting for the promotion warps
+        p.prof[8] = (unsigned long long)wait_tma;   // MMA thread waiting for TMA data
       }
     }
   } else {
     // ------------------------------ promotion + epilogue ------------------------------
-    const int ew = warp - 2;
+    reg_alloc<kEpiRegs>();
+    const int ew = warp - kCtrlWarps;
     const int q = warp & 3;        // TMEM lane quarter this warp may read
     const int h = ew >> 2;         // which half of the tile's columns
     constexpr int CPT = Cfg::kColsPerThread;
     constexpr int CH = Cfg::kChunks;
+    static_assert(CH == 2 || CH == 4, "two or four 32-column chunks per thread");
     uint32_t it = 0;
     bool alive = true;
-    const bool prof_me = p.prof && blockIdx.x == 0 && warp == 2 && lane == 0;
-    const long long t_begin = clock64();
-    long long t_tile_epi = 0, t_tile_head = 0;
+    const bool prof_me = PROF && p.prof && blockIdx.x == 0 && ew == 0 && lane == 0;
+    const long long t_begin = PROF ? clock64() : 0;
+    long long t_wait = 0, t_promote = 0, t_epi = 0;
+    const int nblk_per_expert = p.n_per_expert / kBlockK;
     for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x) {
-      const long long th0 = clock64();
       const int m_tile = w / p.n_tiles, n_tile = w % p.n_tiles;
       const int e = p.tile_expert[m_tile];
       const int row = m_tile * kTileM + q * 32 + lane;
       const int tok = p.row_token[row];
-      float acc[CPT];
+      float2 acc[CPT / 2];
 #pragma unroll
-      for (int j = 0; j < CPT; ++j) acc[j] = 0.f;
+      for (int j = 0; j < CPT / 2; ++j) acc[j] = make_float2(0.f, 0.f);
 
-      // scale pointers
       const float* sa_ptr = nullptr;
       const float* sb0_ptr;
       const float* sb1_ptr = nullptr;
-      const int nblk_per_expert = p.n_per_expert / kBlockK;
       if (MODE == 1) {
         sa_ptr = p.a_scale + row;
         const int gcol0 = n_tile * (BN / 2) + h * (BN / 4);          // first gate row of this thread
         sb0_ptr = p.b_scale + ((size_t)e * nblk_per_expert + gcol0 / kBlockK) * kblocks;
         sb1_ptr = p.b_scale + ((size_t)e * nblk_per_expert + (p.inter + gcol0) / kBlockK) * kblocks;
+#pragma unroll 1
+        for (int kb = 1; kb < kScalePrefetchDist && kb < kblocks; ++kb) prefetch_l2(sa_ptr + (size_t)kb * p.m_cap);
       } else {
         const int col0 = n_tile * BN + h * (BN / 2);
         sb0_ptr = p.b_scale + ((size_t)e * nblk_per_expert + col0 / kBlockK) * kblocks;
@@ -207,7 +236,6 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       float sa_n = MODE == 1 ? sa_ptr[0] : 1.f;
       float sb0_n = sb0_ptr[0];
       float sb1_n = MODE == 1 ? sb1_ptr[0] : 0.f;
-      t_tile_head += clock64() - th0;
 
       for (int kb = 0; kb < kblocks; ++kb, ++it) {
         const uint32_t b = it & 1u, bph = (it >> 1) & 1u;
@@ -217,82 +245,92 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           if (MODE == 1) {
             sa_n = sa_ptr[(size_t)(kb + 1) * p.m_cap];
             sb1_n = sb1_ptr[kb + 1];
+            if (kb + kScalePrefetchDist < kblocks) prefetch_l2(sa_ptr + (size_t)(kb + kScalePrefetchDist) * p.m_cap);
           }
           sb0_n = sb0_ptr[kb + 1];
         }
-        long long c0 = clock64();
+        const long long c0 = PROF ? clock64() : 0;
         bool ok = mbar_wait(bar_tfull + 8 * b, bph, abort_flag, p.status, 4);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { alive = false; break; }
         tc_fence_after();
-        long long c1 = clock64();
-        long long ld_cycles = 0;
+        const long long c1 = PROF ? clock64() : 0;
         const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + b * BN;
-#pragma unroll
-        for (int c = 0; c < CH; ++c) {
-          uint32_t col;
-          float sc;
-          if (MODE == 1) {
-            const bool up = c >= CH / 2;
-            col = (up ? BN / 2 : 0) + h * (BN / 4) + (up ? c - CH / 2 : c) * 32;
-            sc = up ? sc1 : sc0;
-          } else {
-            col = h * (BN / 2) + c * 32;
-            sc = sc0;
-          }
-          uint32_t r[32];
-          long long l0 = clock64();
-          tmem_ld_32x32(t_row + col, r);
-          tmem_ld_wait();
-          ld_cycles += clock64() - l0;
-#pragma unroll
-          for (int j = 0; j < 32; ++j) acc[c * 32 + j] = fmaf(__uint_as_float(r[j]), sc, acc[c * 32 + j]);
+        uint32_t ra[32], rb[32];
+        tmem_ld_32x32(t_row + chunk_col<MODE, BN>(0, h), ra);
+        tmem_ld_32x32(t_row + chunk_col<MODE, BN>(1, h), rb);
+        tmem_ld_wait_on(ra, rb);
+        if constexpr (CH == 2) {
+          fma_chunk(acc, ra, sc0);
+          fma_chunk(acc + 16, rb, MODE == 1 ? sc1 : sc0);
+        } else {
+          fma_chunk(acc, ra, sc0);
+          tmem_ld_32x32(t_row + chunk_col<MODE, BN>(2, h), ra);
+          fma_chunk(acc + 16, rb, sc0);
+          tmem_ld_32x32(t_row + chunk_col<MODE, BN>(3, h), rb);
+          tmem_ld_wait_on(ra, rb);
+          fma_chunk(acc + 32, ra, MODE == 1 ? sc1 : sc0);
+          fma_chunk(acc + 48, rb, MODE == 1 ? sc1 : sc0);
         }
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
-        if (p.prof && blockIdx.x == 0 && warp == 2 && lane == 0) {
-          long long c2 = clock64();
-          atomicAdd((unsigned long long*)p.prof + 0, (unsigned long long)(c1 - c0));   // wait for accumulator
-          atomicAdd((unsigned long long*)p.prof + 1, (unsigned long long)(c2 - c1));   // promotion
-          atomicAdd((unsigned long long*)p.prof + 2, (unsigned long long)ld_cycles);   // of which tcgen05.ld + wait
-          atomicAdd((unsigned long long*)p.prof + 3, 1ull);                            // K blocks
+        if (PROF) {
+          const long long c2 = clock64();
+          t_wait += c1 - c0;
+          t_promote += c2 - c1;
+          if (prof_me && p.trace && it < 64) {
+            p.trace[it * 4 + 2] = (unsigned long long)c1;   // accumulator ready seen by a promotion warp
+            p.trace[it * 4 + 3] = (unsigned long long)c2;   // promotion of this K block done
+          }
         }
       }
       if (!alive) break;
-      const long long te0 = clock64();
+      const long long te0 = PROF ? clock64() : 0;
 
       if (tok >= 0) {
         if (MODE == 1) {
-          // acc[0 .. CPT/2) = gate columns, acc[CPT/2 .. CPT) = matching up columns
-          constexpr int HALF = CPT / 2;
+          // acc pairs [0 .. CPT/4) = gate columns, [CPT/4 .. CPT/2) = matching up columns
+          constexpr int HP = CPT / 4;
           float* dst = p.act + (size_t)row * p.inter + n_tile * (BN / 2) + h * (BN / 4);
           float amax = 0.f;
 #pragma unroll
-          for (int j = 0; j < HALF; j += 4) {
+          for (int j = 0; j < HP; j += 2) {
             float4 v;
-            v.x = silu_mul(acc[j + 0], acc[HALF + j + 0]);
-            v.y = silu_mul(acc[j + 1], acc[HALF + j + 1]);
-            v.z = silu_mul(acc[j + 2], acc[HALF + j + 2]);
-            v.w = silu_mul(acc[j + 3], acc[HALF + j + 3]);
+            v.x = silu_mul(acc[j].x, acc[HP + j].x);
+            v.y = silu_mul(acc[j].y, acc[HP + j].y);
+            v.z = silu_mul(acc[j + 1].x, acc[HP + j + 1].x);
+            v.w = silu_mul(acc[j + 1].y, acc[HP + j + 1].y);
             amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-            *reinterpret_cast<float4*>(dst + j) = v;
+            *reinterpret_cast<float4*>(dst + 2 * j) = v;
           }
           atomicMax(p.row_amax + row, __float_as_uint(amax));
         } else {
           const float rs = p.row_scale[row] * p.row_weight[row];
-          float* dst = p.out_acc + (size_t)tok * p.hidden + n_tile * BN + h * (BN / 2);
+          __nv_bfloat16* dst = p.y + (size_t)row * p.hidden + n_tile * BN + h * (BN / 2);
 #pragma unroll
-          for (int j = 0; j < CPT; j += 4)
-            red_add_v4(dst + j, acc[j] * rs, acc[j + 1] * rs, acc[j + 2] * rs, acc[j + 3] * rs);
+          for (int j = 0; j < CPT / 2; j += 4) {
+            uint4 pk;
+            __nv_bfloat162 t0 = __floats2bfloat162_rn(acc[j].x * rs, acc[j].y * rs);
+            __nv_bfloat162 t1 = __floats2bfloat162_rn(acc[j + 1].x * rs, acc[j + 1].y * rs);
+            __nv_bfloat162 t2 = __floats2bfloat162_rn(acc[j + 2].x * rs, acc[j + 2].y * rs);
+            __nv_bfloat162 t3 = __floats2bfloat162_rn(acc[j + 3].x * rs, acc[j + 3].y * rs);
+            pk.x = *reinterpret_cast<uint32_t*>(&t0);
+            pk.y = *reinterpret_cast<uint32_t*>(&t1);
+            pk.z = *reinterpret_cast<uint32_t*>(&t2);
+            pk.w = *reinterpret_cast<uint32_t*>(&t3);
+            *reinterpret_cast<uint4*>(dst + 2 * j) = pk;
+          }
         }
       }
-      t_tile_epi += clock64() - te0;
+      if (PROF) t_epi += clock64() - te0;
     }
     if (prof_me) {
+      p.prof[0] = (unsigned long long)t_wait;                  // waiting for an accumulator
+      p.prof[1] = (unsigned long long)t_promote;               // TMEM read-back + FMAs
+      p.prof[3] = (unsigned long long)it;                      // K blocks
       p.prof[4] = (unsigned long long)(clock64() - t_begin);   // whole role
-      p.prof[5] = (unsigned long long)t_tile_epi;              // per-tile epilogues
-      p.prof[6] = (unsigned long long)t_tile_head;             // per-tile set-up loads
+      p.prof[5] = (unsigned long long)t_epi;                   // per-tile epilogues
     }
   }
 
@@ -303,13 +341,19 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
 
 template <int MODE, int BN>
 cudaError_t launch_one(const GemmParams& p, int num_sms, cudaStream_t stream) {
-  grouped_gemm_kernel<MODE, BN><<<num_sms, kGemmThreads, TileCfg<BN>::kSmemBytes, stream>>>(p);
+  if (p.prof)
+    grouped_gemm_kernel<MODE, BN, true><<<num_sms, kGemmThreads, TileCfg<BN>::kSmemBytes, stream>>>(p);
+  else
+    grouped_gemm_kernel<MODE, BN, false><<<num_sms, kGemmThreads, TileCfg<BN>::kSmemBytes, stream>>>(p);
   return cudaGetLastError();
 }
 
 template <int MODE, int BN>
 cudaError_t configure_one() {
-  return cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BN, true>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, TileCfg<BN>::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               TileCfg<BN>::kSmemBytes);
 }
 

@@ -37,9 +37,10 @@ struct GemmParams {
   unsigned* row_amax;       // GEMM1 out: bits of max |act| per row
   const float* row_scale;   // GEMM2 in: requantisation scale per row
   const float* row_weight;  // GEMM2 in: routing weight per row
-  float* out_acc;           // GEMM2 out: [T][hidden] fp32, accumulated with red.add
+  __nv_bfloat16* y;         // GEMM2 out: [m_cap][hidden] bf16 rows, already scaled by weight
   int* status;
   unsigned long long* prof;   // optional cycle counters of CTA 0 (null: off)
+  unsigned long long* trace;  // optional [64][4] absolute cycle stamps of CTA 0's first K blocks
 };
 
 // mode 1: GEMM1 + SwiGLU + row amax; mode 2: GEMM2 + weighted combine.  bn: 128 or 256.
@@ -47,8 +48,8 @@ cudaError_t launch_grouped_gemm(int mode, int bn, const GemmParams& p, int num_s
 cudaError_t configure_grouped_gemm();   // opt-in shared memory sizes, once per process and device
 
 cudaError_t launch_requant(const Workspace& ws, int inter, int num_sms, cudaStream_t stream);
-cudaError_t launch_finalize(const float* out_acc, int T, int hidden, void* out_bf16, long long out_row_stride,
-                            int num_sms, cudaStream_t stream);
+cudaError_t launch_combine(const Workspace& ws, int T, int hidden, void* out_bf16, long long out_row_stride,
+                           int num_sms, cudaStream_t stream);
 
 cudaError_t launch_ep_pack(const int32_t* ids, const float* w, const uint8_t* hidden, long long hidden_row_stride,
                            const float* hscale, long long sstride_t, long long sstride_kb, int T, int hidden_dim,

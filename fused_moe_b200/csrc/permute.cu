@@ -9,6 +9,7 @@
 //   scan   : per-expert totals from the per-chunk histogram, 128-padded segment starts,
 //            the M-tile -> expert table, per-chunk bases, padding rows marked -1
 //   place  : one block per 256-token chunk; a warp walks an expert's tokens in order
+//   place  also records, per (token, k), the packed row it went to (-1: expert not local)
 //   gather : one warp per packed row copies the e4m3 row and its 1x128 scales
 #include "common.cuh"
 #include "kernels.cuh"
@@ -85,6 +86,13 @@ place_kernel(Workspace ws, const int32_t* __restrict__ ids, long long ids_stride
   const int* expert_row0 = ws.at<int>(ws.L.expert_row0);
   int* row_token = ws.at<int>(ws.L.row_token);
   float* row_weight = ws.at<float>(ws.L.row_weight);
+  int* tok_rows = ws.at<int>(ws.L.tok_rows);
+  // every (token, k) of the chunk starts as "not local"; local ones are overwritten below
+  for (int i = threadIdx.x; i < kChunkTokens * kTopK; i += blockDim.x) {
+    int t = t0 + i / kTopK;
+    if (t < T) tok_rows[(size_t)t * kTopK + i % kTopK] = -1;
+  }
+  __syncthreads();
   for (int e = warp; e < e_local; e += nwarps) {
     if (chunk_counts[c * e_local + e] == 0) continue;
     int pos = expert_row0[e] + chunk_base[c * e_local + e];
@@ -101,6 +109,7 @@ place_kernel(Workspace ws, const int32_t* __restrict__ ids, long long ids_stride
         int t = t0 + tl;
         row_token[r] = t;
         row_weight[r] = w[(size_t)t * w_stride + kf];
+        tok_rows[(size_t)t * kTopK + kf] = r;
       }
       pos += __popc(hit);
     }
@@ -116,12 +125,14 @@ gather_kernel(Workspace ws, const uint8_t* __restrict__ hidden, long long hidden
   const int* row_token = ws.at<int>(ws.L.row_token);
   uint8_t* a_packed = ws.at<uint8_t>(ws.L.a_packed);
   float* a_scale = ws.at<float>(ws.L.a_scale);
+  unsigned* row_amax = ws.at<unsigned>(ws.L.row_amax);
   const int m_cap = ws.L.m_cap;
   const int vecs = hidden_dim / 16;
   const int kblocks = hidden_dim / kBlockK;
   for (int m = blockIdx.x * warps_per_block + (threadIdx.x >> 5); m < rows; m += gridDim.x * warps_per_block) {
     int t = row_token[m];
     if (t < 0) continue;
+    if (lane == 0) row_amax[m] = 0u;   // GEMM1's epilogue takes the running maximum with atomicMax
     const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)t * hidden_row_stride);
     uint4* dst = reinterpret_cast<uint4*>(a_packed + (size_t)m * hidden_dim);
     for (int v = lane; v < vecs; v += 32) dst[v] = __ldg(src + v);

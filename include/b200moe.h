@@ -76,9 +76,11 @@ typedef struct b200moe_ws_layout {
   uint64_t row_amax;      /* uint32[m_cap]: bits of max|act| per row */
   uint64_t act_q;         /* uint8[m_cap][inter] e4m3 */
   uint64_t row_scale;     /* float[m_cap] */
-  uint64_t out_acc;       /* float[T][hidden] */
+  uint64_t y;             /* bf16[m_cap][hidden]: GEMM2 rows times routing weight */
+  uint64_t tok_rows;      /* int32[T][8]: packed row of (token,k), -1 if the expert is not local */
   uint64_t topk_ids;      /* int32[T][8]  (used by b200moe_run) */
   uint64_t topk_w;        /* float[T][8]  (used by b200moe_run) */
+  uint64_t trace;         /* uint64[2][64][4]: cycle stamps written when B200MOE_PROF is set */
   int32_t m_cap;          /* capacity in packed rows (multiple of 128) */
   int32_t max_tiles;
   int32_t n_chunks;

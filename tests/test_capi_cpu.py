@@ -41,7 +41,7 @@ def test_workspace_layout_is_aligned_ordered_and_grows_with_T():
     prev = 0
     for T in (0, 1, 8, 64, 257, 4096, 16384):
         L = _capi.workspace_layout(T, 32, 7168, 2048)
-        offs = [getattr(L, f) for f, _ in _capi.WsLayout._fields_[1:19]]
+        offs = [getattr(L, f) for f, _ in _capi.WsLayout._fields_[1:21]]
         assert all(o % 256 == 0 for o in offs)
         assert offs == sorted(offs) and len(set(offs)) == len(offs)
         assert L.m_cap % 128 == 0 and L.m_cap >= min(8, 32) * T + 128
