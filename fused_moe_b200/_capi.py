@@ -46,6 +46,9 @@ SIGNATURES = {
     "b200moe_last_cuda_error": (C.c_char_p, []),
     "b200moe_workspace_layout": (_I, [_I, _I, _I, _I, C.POINTER(WsLayout)]),
     "b200moe_route": (_I, [_P, _I, _P, _I, _I, _F, _I, _I, _I, _I, _P, _P, _P, _Z, _P]),
+    "b200moe_route_static": (_I, [_P, _I, _P, _I, _I, _F, _I, _I, _P, _P, _P, _P]),
+    "b200moe_route_static_max_tokens": (_I, []),
+    "b200moe_route_static_error": (C.c_char_p, []),
     "b200moe_count": (_I, [_P, _L, _I, _I, _I, _I, _I, _P, _Z, _P]),
     "b200moe_experts": (_I, [_P, _L, _P, _L, _P, _L, _P, _L, _L, _P, _P, _P, _P,
                              _I, _I, _I, _I, _I, _P, _Z, _P, _L, _P]),

@@ -113,6 +113,28 @@ B200MOE_API int b200moe_route(const void* logits, int logits_dtype, const void* 
                   int32_t* topk_ids, float* topk_w,
                   void* workspace, size_t workspace_bytes, void* stream);
 
+/* Routing without a workspace, for callers that are not allowed to allocate device memory
+ * (an engine plugin's enqueue hook, a serving loop with a frozen memory budget, code that
+ * must avoid the device-wide synchronisation of cudaMalloc).  No counterpart in the
+ * reference, whose host code allocates freely (solution/python/kernel.py:208-329).
+ * Same routing and outputs as b200moe_route (topk_ids int32 [T,8], topk_w float [T,8]);
+ * in addition expert_counts int32[e_local] receives the number of (token,k) pairs per local
+ * expert.  The scratch this needs (a per-chunk histogram) is a fixed 256 KiB array inside
+ * the library image, which every GPU that loads the library holds until the process exits.
+ *  - at most b200moe_route_static_max_tokens() = 65536 tokens per call; larger T returns
+ *    B200MOE_ERR_UNSUPPORTED_SHAPE (text in b200moe_route_static_error) and launches nothing;
+ *  - calls nothing that allocates (no cudaMalloc/cudaFree, no torch);
+ *  - the first call on each device resolves the array's device address
+ *    (cudaGetSymbolAddress, with that device current): make that first call before any
+ *    stream capture begins;
+ *  - all calls on a device share the array: calls that can overlap on the GPU (different
+ *    streams without ordering) race on it and give wrong counts. */
+B200MOE_API int b200moe_route_static(const void* logits, int logits_dtype, const void* bias, int bias_dtype,
+                         int T, float routed_scaling_factor, int local_expert_offset, int e_local,
+                         int32_t* topk_ids, float* topk_w, int32_t* expert_counts, void* stream);
+B200MOE_API int b200moe_route_static_max_tokens(void);
+B200MOE_API const char* b200moe_route_static_error(void);
+
 /* Histogram of local experts for routing that was computed elsewhere (the
  * expert-parallel path, where rows arrive with their ids).  Clears and fills the same
  * workspace counters as b200moe_route.  ids_row_stride in int32 elements. */
