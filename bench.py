@@ -463,7 +463,7 @@ def run_profile_case(args):
     prof = None
     if os.environ.get("B200MOE_PROF"):
         raw = ws.view("meta", torch.int64, (32,)).cpu().numpy()      # meta + its padding, as u64 words
-        names = ("wait_acc", "promote", "unused", "kblocks", "epi_role_total", "tile_epilogues", "unused2",
+        names = ("wait_acc", "promote", "mma_issue", "kblocks", "epi_role_total", "tile_epilogues", "unused2",
                  "mma_wait_epilogue", "mma_wait_tma")
         prof = {"gemm1": dict(zip(names, (int(x) for x in raw[4:13]))),
                 "gemm2": dict(zip(names, (int(x) for x in raw[17:26])))}

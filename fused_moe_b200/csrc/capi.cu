@@ -77,6 +77,8 @@ int ensure_device(int* num_sms) {
     }
     g_dev[dev].num_sms = prop.multiProcessorCount;
     CUDA_TRY(configure_grouped_gemm());
+    CUDA_TRY(configure_grouped_gemm_pair());
+    CUDA_TRY(configure_decode_gemm());
     g_dev[dev].ready = true;
   }
   *num_sms = g_dev[dev].num_sms;
@@ -113,7 +115,8 @@ void compute_layout(int T, int e_local, int hidden, int inter, b200moe_ws_layout
   memset(L, 0, sizeof(*L));
   const int n_chunks = T > 0 ? (T + kChunkTokens - 1) / kChunkTokens : 1;
   const long long pairs = (long long)T * (e_local < kTopK ? e_local : kTopK);
-  const long long m_cap = (long long)align_up((uint64_t)pairs, kTileM) + (long long)kTileM * e_local;
+  // every expert segment may be padded to 256 rows (two M tiles, one per CTA of a pair)
+  const long long m_cap = (long long)align_up((uint64_t)pairs, 2 * kTileM) + (long long)2 * kTileM * e_local;
   L->m_cap = (int32_t)m_cap;
   L->max_tiles = (int32_t)(m_cap / kTileM);
   L->n_chunks = n_chunks;
@@ -131,7 +134,7 @@ void compute_layout(int T, int e_local, int hidden, int inter, b200moe_ws_layout
   L->row_weight = take((uint64_t)m_cap * 4);
   L->a_packed = take((uint64_t)m_cap * hidden);
   L->a_scale = take((uint64_t)(hidden / kBlockK) * m_cap * 4);
-  L->act = take((uint64_t)m_cap * inter * 4);
+  L->act = take((uint64_t)m_cap * inter * 2);
   L->row_amax = take((uint64_t)m_cap * 4);
   L->act_q = take((uint64_t)m_cap * inter);
   L->row_scale = take((uint64_t)m_cap * 4);
@@ -262,18 +265,30 @@ int b200moe_experts(const int32_t* topk_ids, int64_t ids_row_stride, const float
   if ((rc = ensure_device(&num_sms)) != B200MOE_OK) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 
+  // B200MOE_GEMM=pair: CTA pairs (256-row tiles); default: one CTA per tile
+  static const bool use_pairs = [] {
+    const char* v = getenv("B200MOE_GEMM");
+    return v && v[0] == 'p';
+  }();
   CUDA_TRY(launch_permute(ws, topk_ids, ids_row_stride, topk_w, w_row_stride, hidden_states, hidden_row_stride,
                           hidden_scale, scale_stride_t, scale_stride_kb, T, e_local, local_expert_offset, hidden,
-                          num_sms, st));
+                          use_pairs ? 2 * kTileM : kTileM, num_sms, st));
 
   // small problems get the narrower N tile: more work items to spread over the SMs
-  const int bn = (long long)T * kTopK <= 2048 ? 128 : 256;
+  // Up to 64 tokens: swapped-operand decode kernels (B200MOE_DECODE=0 turns them off).
+  static const bool decode_on = [] {
+    const char* v = getenv("B200MOE_DECODE");
+    return !(v && v[0] == '0');
+  }();
+  const int nt = (decode_on && !use_pairs && T <= 64) ? (T <= 16 ? 16 : 64) : 0;
+  const int bn = use_pairs ? 256 : (nt ? 128 : ((long long)T * kTopK <= 2048 ? 128 : 256));
 
   GemmParams g1;
   memset(&g1, 0, sizeof(g1));
   if ((rc = make_tmap(&g1.tmap_a, ws.base + ws.L.a_packed, (uint64_t)ws.L.m_cap, (uint64_t)hidden, (uint64_t)hidden,
-                      kTileM)) != B200MOE_OK)
+                      nt ? nt : kTileM)) != B200MOE_OK)
     return rc;
+  if (use_pairs && (hidden % 256 != 0 || inter % 128 != 0)) return B200MOE_ERR_UNSUPPORTED_SHAPE;
   if ((rc = make_tmap(&g1.tmap_b, w1, (uint64_t)e_local * 2 * inter, (uint64_t)hidden, (uint64_t)hidden, bn / 2)) !=
       B200MOE_OK)
     return rc;
@@ -285,10 +300,11 @@ int b200moe_experts(const int32_t* topk_ids, int64_t ids_row_stride, const float
   g1.m_cap = ws.L.m_cap;
   g1.n_per_expert = 2 * inter;
   g1.kblocks = hidden / kBlockK;
-  g1.n_tiles = inter / (bn / 2);
+  g1.n_tiles = nt ? inter / 64 : inter / (bn / 2);
+  g1.expert_count = ws.at<int>(ws.L.expert_count);
   g1.inter = inter;
   g1.hidden = hidden;
-  g1.act = ws.at<float>(ws.L.act);
+  g1.act = ws.at<__half>(ws.L.act);
   g1.row_amax = ws.at<unsigned>(ws.L.row_amax);
   g1.status = ws.at<int>(ws.L.status);
   // B200MOE_PROF=1: CTA 0 adds cycle counters into the padding after `meta`
@@ -297,7 +313,9 @@ int b200moe_experts(const int32_t* topk_ids, int64_t ids_row_stride, const float
   g1.prof = prof_on ? ws.at<unsigned long long>(ws.L.meta + 32) : nullptr;
   g1.trace = prof_on ? ws.at<unsigned long long>(ws.L.trace) : nullptr;
   if (g_prof_start) CUDA_TRY(cudaEventRecord(g_prof_start, st));
-  CUDA_TRY(launch_grouped_gemm(1, bn, g1, num_sms, st));
+  if (nt) CUDA_TRY(launch_decode_gemm(1, nt, g1, num_sms, st));
+  else if (use_pairs) CUDA_TRY(launch_grouped_gemm_pair(1, g1, num_sms, st));
+  else CUDA_TRY(launch_grouped_gemm(1, bn, g1, num_sms, st));
   if (g_prof_stop) CUDA_TRY(cudaEventRecord(g_prof_stop, st));
   g_prof_start = g_prof_stop = nullptr;
 
@@ -306,7 +324,7 @@ int b200moe_experts(const int32_t* topk_ids, int64_t ids_row_stride, const float
   GemmParams g2;
   memset(&g2, 0, sizeof(g2));
   if ((rc = make_tmap(&g2.tmap_a, ws.base + ws.L.act_q, (uint64_t)ws.L.m_cap, (uint64_t)inter, (uint64_t)inter,
-                      kTileM)) != B200MOE_OK)
+                      nt ? nt : kTileM)) != B200MOE_OK)
     return rc;
   if ((rc = make_tmap(&g2.tmap_b, w2, (uint64_t)e_local * hidden, (uint64_t)inter, (uint64_t)inter, bn / 2)) !=
       B200MOE_OK)
@@ -318,7 +336,8 @@ int b200moe_experts(const int32_t* topk_ids, int64_t ids_row_stride, const float
   g2.m_cap = ws.L.m_cap;
   g2.n_per_expert = hidden;
   g2.kblocks = inter / kBlockK;
-  g2.n_tiles = hidden / bn;
+  g2.n_tiles = nt ? hidden / 128 : hidden / bn;
+  g2.expert_count = g1.expert_count;
   g2.inter = inter;
   g2.hidden = hidden;
   g2.row_scale = ws.at<float>(ws.L.row_scale);
@@ -327,7 +346,9 @@ int b200moe_experts(const int32_t* topk_ids, int64_t ids_row_stride, const float
   g2.status = g1.status;
   g2.prof = prof_on ? ws.at<unsigned long long>(ws.L.meta + 136) : nullptr;
   g2.trace = prof_on ? ws.at<unsigned long long>(ws.L.trace) + 4 * 64 : nullptr;
-  CUDA_TRY(launch_grouped_gemm(2, bn, g2, num_sms, st));
+  if (nt) CUDA_TRY(launch_decode_gemm(2, nt, g2, num_sms, st));
+  else if (use_pairs) CUDA_TRY(launch_grouped_gemm_pair(2, g2, num_sms, st));
+  else CUDA_TRY(launch_grouped_gemm(2, bn, g2, num_sms, st));
 
   CUDA_TRY(launch_combine(ws, T, hidden, out_bf16, out_row_stride, num_sms, st));
   return B200MOE_OK;

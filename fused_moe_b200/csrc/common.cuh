@@ -147,6 +147,44 @@ __device__ __forceinline__ void tc_mma_f8(uint32_t d_tmem, uint64_t a_desc, uint
       : "memory");
 }
 
+// Four MMAs (K = 4 x 32) of one 128-wide K block in a single instruction sequence: the first
+// overwrites the accumulator, the others add.  The issuing thread runs alone, so every
+// instruction it spends is on the critical path; descriptors are therefore passed as
+// prebuilt 32-bit halves (low word = start address >> 4 plus constants, see
+// make_kmajor_sw128_desc) and advanced by 32 bytes (2 units) in place.
+__device__ __forceinline__ void tc_mma_f8_kblock(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                                 uint32_t idesc) {
+  asm volatile(
+      "{\n\t.reg .pred pf, pt;\n\t.reg .b64 da, db;\n\t.reg .b32 al, bl;\n\t"
+      "setp.ne.b32 pf, 0, 0;\n\t"
+      "setp.eq.b32 pt, 0, 0;\n\t"
+      "mov.b64 da, {%1, %3};\n\t"
+      "mov.b64 db, {%2, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, pf;\n\t"
+      "add.u32 al, %1, 2;\n\t"
+      "add.u32 bl, %2, 2;\n\t"
+      "mov.b64 da, {al, %3};\n\t"
+      "mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, pt;\n\t"
+      "add.u32 al, %1, 4;\n\t"
+      "add.u32 bl, %2, 4;\n\t"
+      "mov.b64 da, {al, %3};\n\t"
+      "mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, pt;\n\t"
+      "add.u32 al, %1, 6;\n\t"
+      "add.u32 bl, %2, 6;\n\t"
+      "mov.b64 da, {al, %3};\n\t"
+      "mov.b64 db, {bl, %3};\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %4, pt;\n\t}"
+      ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc)
+      : "memory");
+}
+// Halves of make_kmajor_sw128_desc(smem_addr): low word for an address, and the constant high word.
+__device__ __forceinline__ uint32_t kmajor_sw128_desc_lo(uint32_t smem_addr) {
+  return ((smem_addr & 0x3FFFFu) >> 4) | (1u << 16);
+}
+constexpr uint32_t kKmajorSw128DescHi = (uint32_t)(1024 >> 4) | (1u << 14) | (2u << 29);
+
 // Shared-memory matrix descriptor for a K-major operand tile stored as rows of 128 bytes
 // with the 128-byte swizzle (what a TMA box with a 128-byte inner extent produces):
 // 8-row groups are 1024 bytes apart (stride byte offset), leading byte offset unused (1).
@@ -209,8 +247,113 @@ template <int N> __device__ __forceinline__ void reg_dealloc() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
 }
 
+__device__ __forceinline__ void prefetch_l1(const void* p) {
+  asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
+}
 __device__ __forceinline__ void prefetch_l2(const void* p) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
+// ---- CTA pairs (thread-block cluster of two, tcgen05 cta_group::2) ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of `smem_addr` (a shared::cta address) inside CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Arrive without a release: for signals that order nothing but register-resident results
+// (e.g. "this accumulator has been read back": tcgen05.wait::ld already completed the reads).
+// A cluster-scope release would first wait for every global load the thread has in flight.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx_cluster(uint32_t cluster_addr, uint32_t bytes) {
+  // relaxed: the producer publishes no data of its own; the copies' complete_tx orders the bytes
+  asm volatile("mbarrier.arrive.expect_tx.relaxed.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(cluster_addr), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait_cluster(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done;
+}
+// Bounded wait with cluster-scope acquire (the data guarded may live in the peer CTA).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                  int* status, int where) {
+  long long t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    if (++spins >= 128u) {
+      spins = 0;
+      if (*abort_flag) return false;
+      long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitBudgetCycles) {
+        *abort_flag = 1;
+        if (atomicCAS(status + kStatusCode, 0, (int)B200MOE_ERR_DEVICE_TIMEOUT) == 0)
+          status[kStatusDetail] = where;
+        return false;
+      }
+    }
+  }
+}
+// TMA load into this CTA's shared memory whose completion bytes are counted on an mbarrier
+// that may live in the peer CTA of the pair (`mbar_cluster_addr` from map_to_cta).
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t smem_dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t mbar_cluster_addr) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(mbar_cluster_addr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_result_addr, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result_addr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// One MMA over both CTAs of the pair: rows 0-127 of D/A in the leader, 128-255 in its peer;
+// each CTA holds its half of B's rows.  Issued by one thread of the leader CTA.
+__device__ __forceinline__ void tc_mma_f8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Completion of this thread's MMAs, signalled on the barrier at the same offset in every CTA of `cta_mask`.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t cta_mask) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"(cta_mask)
+               : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair_local(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {

@@ -3,10 +3,12 @@
 // requant replaces the back half of the reference's `swiglu_fp8_requant_kernel`
 // (solution/python/moe_fused.cu:175-195): one scale per row, scale = max(amax/448, 1e-8),
 // values rounded to nearest even.  The row maximum comes from GEMM1's epilogue, so the
-// fp32 activations are read exactly once here.
+// fp16 activations are read exactly once here.
 // combine replaces `reduce_scatter_from_2d_perm_kernel` / `weighted_scatter_kernel`
 // (moe_fused.cu:346-393, 490-517): a gather per token over its rows instead of atomics,
 // so the output is bit-reproducible.
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -21,26 +23,33 @@ __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float 
   return lo | (hi << 16);
 }
 
+// One block per packed row (grid-stride): a row is 2-8 KB, so one warp walking it alone would
+// be a chain of dependent global loads; 256 threads fetch it in one or two rounds.
 __global__ void __launch_bounds__(256)
 requant_kernel(Workspace ws, int inter) {
-  const int lane = threadIdx.x & 31;
-  const int wpb = blockDim.x >> 5;
   const int rows = ws.at<int>(ws.L.meta)[1];
   const int* row_token = ws.at<int>(ws.L.row_token);
-  const float* act = ws.at<float>(ws.L.act);
+  const __half* act = ws.at<__half>(ws.L.act);
   const unsigned* row_amax = ws.at<unsigned>(ws.L.row_amax);
   uint8_t* act_q = ws.at<uint8_t>(ws.L.act_q);
   float* row_scale = ws.at<float>(ws.L.row_scale);
-  for (int m = blockIdx.x * wpb + (threadIdx.x >> 5); m < rows; m += gridDim.x * wpb) {
+  for (int m = blockIdx.x; m < rows; m += gridDim.x) {
     if (row_token[m] < 0) continue;
-    float amax = fmaxf(__uint_as_float(row_amax[m]), 1e-8f);
-    float scale = fmaxf(amax / 448.0f, 1e-8f);
-    if (lane == 0) row_scale[m] = scale;
-    const float4* src = reinterpret_cast<const float4*>(act + (size_t)m * inter);
-    uint32_t* dst = reinterpret_cast<uint32_t*>(act_q + (size_t)m * inter);
-    for (int v = lane; v < inter / 4; v += 32) {
-      float4 x = src[v];
-      dst[v] = pack4_e4m3(x.x / scale, x.y / scale, x.z / scale, x.w / scale);
+    const float amax = fmaxf(__uint_as_float(row_amax[m]), 1e-8f);
+    const float scale = fmaxf(amax / 448.0f, 1e-8f);
+    if (threadIdx.x == 0) row_scale[m] = scale;
+    const uint4* src = reinterpret_cast<const uint4*>(act + (size_t)m * inter);   // 8 halves
+    uint2* dst = reinterpret_cast<uint2*>(act_q + (size_t)m * inter);
+    for (int v = threadIdx.x; v < inter / 8; v += blockDim.x) {
+      const uint4 raw = src[v];
+      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+      const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+      const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&raw.z));
+      const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&raw.w));
+      uint2 pk;
+      pk.x = pack4_e4m3(a.x / scale, a.y / scale, b.x / scale, b.y / scale);
+      pk.y = pack4_e4m3(c.x / scale, c.y / scale, d.x / scale, d.y / scale);
+      dst[v] = pk;
     }
   }
 }
@@ -99,9 +108,7 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ tok_
 
 cudaError_t launch_requant(const Workspace& ws, int inter, int num_sms, cudaStream_t stream) {
   long long cap_rows = ws.L.m_cap;
-  int blocks = (int)((cap_rows + 7) / 8);
-  int cap = num_sms * 8;
-  if (blocks > cap) blocks = cap;
+  int blocks = (int)(cap_rows < (long long)num_sms * 16 ? cap_rows : (long long)num_sms * 16);
   requant_kernel<<<blocks, 256, 0, stream>>>(ws, inter);
   return cudaGetLastError();
 }

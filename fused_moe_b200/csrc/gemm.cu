@@ -8,7 +8,7 @@
 // One CTA per SM walks work items (M tile of 128 packed rows, N tile of BN weight rows).
 // Per 128-wide K block (= one fp32 scale block, = one 128-byte swizzled TMA row):
 //   warp 0      TMA producer: A box 128x128 B and two B boxes (BN/2)x128 B into a smem ring
-//   warp 1      issues 4 tcgen05.mma (K=32 each) into one of two TMEM accumulators, starting
+//   warps 1, 2  (one lane each, alternate K blocks) issue 4 tcgen05.mma (K=32 each) into one of two TMEM accumulators, starting
 //               from zero, so each accumulator holds the raw e4m3 dot product of one K block
 //   warps 4-11  read that accumulator back (tcgen05.ld, two loads in flight) and fold it into
 //               fp32 registers with packed FMAs: acc += (a_scale * b_scale) * partial.  The
@@ -16,11 +16,13 @@
 // The control warpgroup (warps 0-3) gives registers back (setmaxnreg) so that the eight
 // promotion warps can hold a 128x256 fp32 tile (128 accumulators per thread) without spills.
 // GEMM1 pairs gate rows [n, n+BN/2) with up rows [inter+n, ...) in one tile, so the epilogue
-// computes g*silu(u) in registers, stores fp32 activations and the row maximum.
+// computes g*silu(u) in registers, stores fp16 activations and the row maximum.
 // GEMM2's epilogue multiplies by (row requant scale * routing weight) and stores the row as
 // bf16; the combine kernel sums a token's rows.
 //
 // Every wait is bounded (see mbar_wait); on a timeout the CTA drains and frees its TMEM.
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 #include "kernels.cuh"
 
@@ -48,7 +50,7 @@ template <int BN> struct TileCfg {
 };
 
 __device__ __forceinline__ float silu_mul(float g, float u) {
-  float sig = 1.0f / (1.0f + __expf(-u));
+  float sig = __fdividef(1.0f, 1.0f + __expf(-u));   // approximate reciprocal: 2 ulp, far below e4m3 resolution
   return g * (u * sig);
 }
 
@@ -84,8 +86,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   const uint32_t bar_empty = bar_full + 8 * S;           // S barriers: stage consumed by the MMAs
   const uint32_t bar_tfull = bar_empty + 8 * S;          // 2 barriers: accumulator written
   const uint32_t bar_tempty = bar_tfull + 16;            // 2 barriers: accumulator read back
-  const uint32_t bar_drain = bar_tempty + 16;            // 1 barrier: all MMAs retired (teardown)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 5);
+  const uint32_t bar_drain = bar_tempty + 16;            // 2 barriers: each issuer's MMAs retired (teardown)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 6);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -101,6 +103,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       mbar_init(bar_tempty + 8 * b, kEpiWarps);
     }
     mbar_init(bar_drain, 1);
+    mbar_init(bar_drain + 8, 1);
     abort_flag[0] = 0;
     abort_flag[1] = 0;   // never set by others: the teardown waits ignore an abort
     fence_mbar_init();
@@ -152,47 +155,47 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t first = it > (uint32_t)S ? it - S : 0u;
       for (uint32_t j = first; j < it; ++j)
         (void)mbar_wait(bar_full + 8 * (j % S), (j / S) & 1u, abort_flag + 1, p.status, 6);
-    } else if (warp == 1 && lane == 0) {
-      // ------------------------------ MMA issuer ------------------------------
+    } else if ((warp == 1 || warp == 2) && lane == 0) {
+      // ------------------------------ MMA issuers ------------------------------
+      // Two threads (on different SM sub-partitions) take alternate K blocks.  Issuing the
+      // four MMAs and two commits of a K block costs one thread ~300 cycles whatever the
+      // tile size, and its waits for operands and for a free accumulator add to that; with
+      // two issuers one waits while the other issues.  Issuer i always writes accumulator i.
       constexpr uint32_t idesc = make_idesc_e4m3(kTileM, BN);
+      const uint32_t me = (uint32_t)(warp - 1);
       uint32_t it = 0;
       bool alive = true;
-      long long wait_epi = 0, wait_tma = 0;
+      long long wait_epi = 0, wait_tma = 0, t_issue = 0;
       for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x) {
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          if ((it & 1u) != me) continue;
           const uint32_t s = it % S, ph = (it / S) & 1u;
-          const uint32_t b = it & 1u, bph = (it >> 1) & 1u;
+          const uint32_t b = me, bph = (it >> 1) & 1u;
           const long long m0 = PROF ? clock64() : 0;
           if (!mbar_wait(bar_tempty + 8 * b, bph ^ 1u, abort_flag, p.status, 2)) { alive = false; break; }
           const long long m1 = PROF ? clock64() : 0;
           if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 3)) { alive = false; break; }
-          if (PROF) {
-            wait_epi += m1 - m0;
-            wait_tma += clock64() - m1;
-            if (p.trace && blockIdx.x == 0 && it < 64) {
-              p.trace[it * 4 + 0] = (unsigned long long)m1;          // accumulator free seen by the MMA thread
-              p.trace[it * 4 + 1] = (unsigned long long)clock64();   // operands landed seen by the MMA thread
-            }
-          }
+          const long long m2 = PROF ? clock64() : 0;
           tc_fence_after();
           const uint32_t a_addr = smem_base + s * Cfg::kStageBytes;
-          const uint32_t b_addr = a_addr + kABytes;
-          const uint32_t d_addr = tmem_base + b * BN;
-#pragma unroll
-          for (int k4 = 0; k4 < kBlockK / 32; ++k4) {
-            tc_mma_f8(d_addr, make_kmajor_sw128_desc(a_addr + k4 * 32), make_kmajor_sw128_desc(b_addr + k4 * 32),
-                      idesc, k4 > 0 ? 1u : 0u);
-          }
+          tc_mma_f8_kblock(tmem_base + b * BN, kmajor_sw128_desc_lo(a_addr), kmajor_sw128_desc_lo(a_addr + kABytes),
+                           kKmajorSw128DescHi, idesc);
           tc_commit(bar_empty + 8 * s);
           tc_commit(bar_tfull + 8 * b);
+          if (PROF) {
+            wait_epi += m1 - m0;
+            wait_tma += m2 - m1;
+            t_issue += clock64() - m2;
+          }
         }
       }
       // All MMAs must retire before TMEM is freed.
-      tc_commit(bar_drain);
-      (void)mbar_wait(bar_drain, 0u, abort_flag + 1, p.status, 5);
-      if (PROF && p.prof && blockIdx.x == 0) {
-        p.prof[7] = (unsigned long long)wait_epi;   // MMA thread waiting for the promotion warps
-        p.prof[8] = (unsigned long long)wait_tma;   // MMA thread waiting for TMA data
+      tc_commit(bar_drain + 8 * me);
+      (void)mbar_wait(bar_drain + 8 * me, 0u, abort_flag + 1, p.status, 5);
+      if (PROF && p.prof && blockIdx.x == 0 && me == 0) {
+        p.prof[7] = (unsigned long long)wait_epi;   // issuer 0 waiting for the promotion warps
+        p.prof[8] = (unsigned long long)wait_tma;   // issuer 0 waiting for TMA data
+        p.prof[2] = (unsigned long long)t_issue;    // issuer 0 issuing MMAs and commits
       }
     }
   } else {
@@ -228,26 +231,43 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         sb0_ptr = p.b_scale + ((size_t)e * nblk_per_expert + gcol0 / kBlockK) * kblocks;
         sb1_ptr = p.b_scale + ((size_t)e * nblk_per_expert + (p.inter + gcol0) / kBlockK) * kblocks;
 #pragma unroll 1
-        for (int kb = 1; kb < kScalePrefetchDist && kb < kblocks; ++kb) prefetch_l2(sa_ptr + (size_t)kb * p.m_cap);
+        for (int kb = 4; kb < 4 + kScalePrefetchDist && kb < kblocks; ++kb) prefetch_l2(sa_ptr + (size_t)kb * p.m_cap);
       } else {
         const int col0 = n_tile * BN + h * (BN / 2);
         sb0_ptr = p.b_scale + ((size_t)e * nblk_per_expert + col0 / kBlockK) * kblocks;
       }
-      float sa_n = MODE == 1 ? sa_ptr[0] : 1.f;
-      float sb0_n = sb0_ptr[0];
-      float sb1_n = MODE == 1 ? sb1_ptr[0] : 0.f;
+      // Scales of K blocks kb .. kb+3 ride in registers: a load issued only one K block ahead
+      // is still in flight when it is needed (L2 under the weight stream answers in ~1 us).
+      constexpr int kScaleAhead = 3;
+      float sa_r[kScaleAhead + 1], sb0_r[kScaleAhead + 1], sb1_r[kScaleAhead + 1];
+#pragma unroll
+      for (int i = 0; i <= kScaleAhead; ++i) {
+        const bool in = i < kblocks;
+        sa_r[i] = (MODE == 1 && in) ? sa_ptr[(size_t)i * p.m_cap] : 1.f;
+        sb0_r[i] = in ? sb0_ptr[i] : 0.f;
+        sb1_r[i] = (MODE == 1 && in) ? sb1_ptr[i] : 0.f;
+      }
 
       for (int kb = 0; kb < kblocks; ++kb, ++it) {
         const uint32_t b = it & 1u, bph = (it >> 1) & 1u;
-        const float sc0 = sa_n * sb0_n;
-        const float sc1 = sa_n * sb1_n;
-        if (kb + 1 < kblocks) {
-          if (MODE == 1) {
-            sa_n = sa_ptr[(size_t)(kb + 1) * p.m_cap];
-            sb1_n = sb1_ptr[kb + 1];
-            if (kb + kScalePrefetchDist < kblocks) prefetch_l2(sa_ptr + (size_t)(kb + kScalePrefetchDist) * p.m_cap);
+        const float sc0 = sa_r[0] * sb0_r[0];
+        const float sc1 = sa_r[0] * sb1_r[0];
+#pragma unroll
+        for (int i = 0; i < kScaleAhead; ++i) {
+          sa_r[i] = sa_r[i + 1];
+          sb0_r[i] = sb0_r[i + 1];
+          sb1_r[i] = sb1_r[i + 1];
+        }
+        {
+          const int nk = kb + kScaleAhead + 1;
+          if (nk < kblocks) {
+            if (MODE == 1) {
+              sa_r[kScaleAhead] = sa_ptr[(size_t)nk * p.m_cap];
+              sb1_r[kScaleAhead] = sb1_ptr[nk];
+              if (nk + kScalePrefetchDist < kblocks) prefetch_l2(sa_ptr + (size_t)(nk + kScalePrefetchDist) * p.m_cap);
+            }
+            sb0_r[kScaleAhead] = sb0_ptr[nk];
           }
-          sb0_n = sb0_ptr[kb + 1];
         }
         const long long c0 = PROF ? clock64() : 0;
         bool ok = mbar_wait(bar_tfull + 8 * b, bph, abort_flag, p.status, 4);
@@ -260,7 +280,12 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         tmem_ld_32x32(t_row + chunk_col<MODE, BN>(0, h), ra);
         tmem_ld_32x32(t_row + chunk_col<MODE, BN>(1, h), rb);
         tmem_ld_wait_on(ra, rb);
+        // The accumulator is free as soon as its last column sits in registers: signal the MMA
+        // thread before the remaining FMAs, which then overlap the next K block's MMAs.
         if constexpr (CH == 2) {
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
           fma_chunk(acc, ra, sc0);
           fma_chunk(acc + 16, rb, MODE == 1 ? sc1 : sc0);
         } else {
@@ -269,12 +294,12 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           fma_chunk(acc + 16, rb, sc0);
           tmem_ld_32x32(t_row + chunk_col<MODE, BN>(3, h), rb);
           tmem_ld_wait_on(ra, rb);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
           fma_chunk(acc + 32, ra, MODE == 1 ? sc1 : sc0);
           fma_chunk(acc + 48, rb, MODE == 1 ? sc1 : sc0);
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
         if (PROF) {
           const long long c2 = clock64();
           t_wait += c1 - c0;
@@ -292,17 +317,23 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         if (MODE == 1) {
           // acc pairs [0 .. CPT/4) = gate columns, [CPT/4 .. CPT/2) = matching up columns
           constexpr int HP = CPT / 4;
-          float* dst = p.act + (size_t)row * p.inter + n_tile * (BN / 2) + h * (BN / 4);
+          // fp16 keeps 11 significant bits, three more than the e4m3 codes made from it need;
+          // the row maximum is taken over the rounded values so that it is attained exactly.
+          __half* dst = p.act + (size_t)row * p.inter + n_tile * (BN / 2) + h * (BN / 4);
           float amax = 0.f;
 #pragma unroll
-          for (int j = 0; j < HP; j += 2) {
-            float4 v;
-            v.x = silu_mul(acc[j].x, acc[HP + j].x);
-            v.y = silu_mul(acc[j].y, acc[HP + j].y);
-            v.z = silu_mul(acc[j + 1].x, acc[HP + j + 1].x);
-            v.w = silu_mul(acc[j + 1].y, acc[HP + j + 1].y);
-            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
-            *reinterpret_cast<float4*>(dst + 2 * j) = v;
+          for (int j = 0; j < HP; j += 4) {
+            uint4 pk;
+            uint32_t* w = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+              __half2 hh = __floats2half2_rn(silu_mul(acc[j + t].x, acc[HP + j + t].x),
+                                             silu_mul(acc[j + t].y, acc[HP + j + t].y));
+              float2 back = __half22float2(hh);
+              amax = fmaxf(amax, fmaxf(fabsf(back.x), fabsf(back.y)));
+              w[t] = *reinterpret_cast<uint32_t*>(&hh);
+            }
+            *reinterpret_cast<uint4*>(dst + 2 * j) = pk;
           }
           atomicMax(p.row_amax + row, __float_as_uint(amax));
         } else {

@@ -1,0 +1,331 @@
+// Decode-size grouped FP8 GEMMs (at most 64 tokens per call): operands swapped.
+//
+// With a handful of rows per expert the layer is a stream of expert weights through the SMs
+// (44 MB per active expert), so the tile is turned around: the 128 MMA rows (TMEM lanes) are
+// 128 WEIGHT rows and the MMA's N dimension is the expert's token rows (16 or 64, all of
+// them, since an expert cannot hold more rows than the call has tokens).  Per 128-wide K
+// block a CTA then moves 16 KB of weights and only NT x 128 B of activations, the MMA and the
+// read-back are a few dozen cycles, four small accumulators rotate in tensor memory, and
+// 8-10 stages of weights are in flight per SM.  Arithmetic is the one of gemm.cu (which
+// replaces the reference's `moe_blockwise_grouped_mm_v2`, solution/python/moe_gemm.cu:527-654,
+// whose own small-batch configuration also swaps A and B, moe_gemm.cu:614-648): raw e4m3 dot
+// product per K block, promoted in fp32 registers with the fp32 block scales.
+//
+// Work item = (expert tile, slab of 128 weight rows).  GEMM1's slab is 64 gate rows plus the
+// 64 matching up rows, so lanes 0-63 hold g and lanes 64-127 hold u of the same columns; the
+// up warps hand u over through shared memory and the gate warps write g*silu(u) (fp16) and
+// the row maxima.  GEMM2's slab is 128 output columns; its epilogue writes bf16(acc * row
+// scale * routing weight).  Stores are token-major: a warp writes 32 consecutive columns of
+// one token row per instruction.
+#include <cuda_fp16.h>
+
+#include "common.cuh"
+#include "kernels.cuh"
+
+namespace b200moe {
+
+namespace {
+
+constexpr int kThreads = 256;            // warps 0-3 control (0: TMA, 1 and 2: MMA), warps 4-7 promotion
+constexpr int kSlabRows = 128;
+constexpr int kWBytes = kSlabRows * kBlockK;   // 16 KiB of weights per stage
+constexpr int kRing = 4;                 // accumulators in tensor memory
+
+template <int NT> struct DCfg {
+  static constexpr int kTokBytes = NT * kBlockK;
+  static constexpr int kStageBytes = kWBytes + kTokBytes;
+  static constexpr int kStages = (NT <= 16) ? 10 : 8;
+  static constexpr int kTmemCols = (kRing * NT < 32) ? 32 : kRing * NT;
+  static constexpr int kXchBytes = 64 * NT * 4;                 // u values of 64 up rows
+  static constexpr int kSmemBytes = kStages * kStageBytes + kXchBytes + 512 + 1024;
+};
+
+__device__ __forceinline__ float silu_mul_d(float g, float u) {
+  float sig = __fdividef(1.0f, 1.0f + __expf(-u));
+  return g * (u * sig);
+}
+
+// 32 lanes x 16 consecutive fp32 columns
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait_on16(uint32_t (&a)[16]) {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" : B200MOE_RW8(a, 0), B200MOE_RW8(a, 8) : : "memory");
+}
+
+template <int MODE, int NT>
+__global__ void __launch_bounds__(kThreads, 1)
+decode_gemm_kernel(const __grid_constant__ GemmParams p) {
+  using Cfg = DCfg<NT>;
+  constexpr int S = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const uint32_t smem_base = smem_u32(smem);
+  float* xch = reinterpret_cast<float*>(smem + S * Cfg::kStageBytes);               // [64][NT]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes + Cfg::kXchBytes);
+  const uint32_t bar_full = smem_u32(bars);
+  const uint32_t bar_empty = bar_full + 8 * S;
+  const uint32_t bar_tfull = bar_empty + 8 * S;
+  const uint32_t bar_tempty = bar_tfull + 8 * kRing;
+  const uint32_t bar_drain = bar_tempty + 8 * kRing;
+  const uint32_t bar_xready = bar_drain + 16;    // 2 barriers: u of an up warp is in shared memory
+  const uint32_t bar_xfree = bar_xready + 16;    // 2 barriers: its gate warp has read it
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 2 * kRing + 6);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < kRing; ++b) {
+      mbar_init(bar_tfull + 8 * b, 1);
+      mbar_init(bar_tempty + 8 * b, 4);
+    }
+    mbar_init(bar_drain, 1);
+    mbar_init(bar_drain + 8, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(bar_xready + 8 * i, 1);
+      mbar_init(bar_xfree + 8 * i, 1);
+    }
+    abort_flag[0] = 0;
+    abort_flag[1] = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&p.tmap_a);
+    tma_prefetch_desc(&p.tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int m_tiles = p.meta[0];
+  const int total_items = m_tiles * p.n_tiles;
+  const int kblocks = p.kblocks;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ------------------------------ TMA producer ------------------------------
+      uint32_t it = 0;
+      bool alive = true;
+      for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x) {
+        const int m_tile = w / p.n_tiles, slab = w % p.n_tiles;
+        const int e = p.tile_expert[m_tile];
+        int wrow0, wrow1;
+        if (MODE == 1) {
+          wrow0 = e * p.n_per_expert + slab * 64;        // 64 gate rows
+          wrow1 = wrow0 + p.inter;                       // the matching 64 up rows
+        } else {
+          wrow0 = e * p.n_per_expert + slab * kSlabRows;
+          wrow1 = wrow0 + 64;
+        }
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          const uint32_t s = it % S, ph = (it / S) & 1u;
+          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status, 21)) { alive = false; break; }
+          const uint32_t full = bar_full + 8 * s;
+          const uint32_t w_dst = smem_base + s * Cfg::kStageBytes;
+          mbar_arrive_expect_tx(full, Cfg::kStageBytes);
+          tma_load_2d(w_dst, &p.tmap_b, kb * kBlockK, wrow0, full);
+          tma_load_2d(w_dst + 64 * kBlockK, &p.tmap_b, kb * kBlockK, wrow1, full);
+          tma_load_2d(w_dst + kWBytes, &p.tmap_a, kb * kBlockK, m_tile * kTileM, full);
+        }
+      }
+      const uint32_t first = it > (uint32_t)S ? it - S : 0u;
+      for (uint32_t j = first; j < it; ++j)
+        (void)mbar_wait(bar_full + 8 * (j % S), (j / S) & 1u, abort_flag + 1, p.status, 26);
+    }
+  } else if (warp == 1 || warp == 2) {
+    if (lane == 0) {
+      // ------------------------------ MMA issuers (alternate K blocks) ------------------------------
+      constexpr uint32_t idesc = make_idesc_e4m3(kSlabRows, NT);
+      const uint32_t me = (uint32_t)(warp - 1);
+      uint32_t it = 0;
+      bool alive = true;
+      for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x) {
+        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          if ((it & 1u) != me) continue;
+          const uint32_t s = it % S, ph = (it / S) & 1u;
+          const uint32_t b = it % kRing, bph = (it / kRing) & 1u;
+          if (!mbar_wait(bar_tempty + 8 * b, bph ^ 1u, abort_flag, p.status, 22)) { alive = false; break; }
+          if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 23)) { alive = false; break; }
+          tc_fence_after();
+          const uint32_t w_addr = smem_base + s * Cfg::kStageBytes;
+          tc_mma_f8_kblock(tmem_base + b * NT, kmajor_sw128_desc_lo(w_addr), kmajor_sw128_desc_lo(w_addr + kWBytes),
+                           kKmajorSw128DescHi, idesc);
+          tc_commit(bar_empty + 8 * s);
+          tc_commit(bar_tfull + 8 * b);
+        }
+      }
+      tc_commit(bar_drain + 8 * me);
+      (void)mbar_wait(bar_drain + 8 * me, 0u, abort_flag + 1, p.status, 25);
+    }
+  } else if (warp >= 4) {
+    // ------------------------------ promotion + epilogue ------------------------------
+    const int q = warp & 3;                 // TMEM lane quarter: weight rows 32q .. 32q+31 of the slab
+    uint32_t it = 0, xi = 0;
+    bool alive = true;
+    const int nblk_per_expert = p.n_per_expert / kBlockK;
+    for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x) {
+      const int m_tile = w / p.n_tiles, slab = w % p.n_tiles;
+      const int e = p.tile_expert[m_tile];
+      const int row0 = m_tile * kTileM;     // the expert's first packed row; its rows are row0 .. row0+cnt-1
+      float acc[NT];
+#pragma unroll
+      for (int j = 0; j < NT; ++j) acc[j] = 0.f;
+
+      // weight-scale block of this warp's rows
+      int wblock;
+      if (MODE == 1) wblock = (q < 2) ? (slab * 64) / kBlockK : (p.inter + slab * 64) / kBlockK;
+      else wblock = slab;
+      const float* sb_ptr = p.b_scale + ((size_t)e * nblk_per_expert + wblock) * kblocks;
+      const float* sa_ptr = MODE == 1 ? p.a_scale + row0 : nullptr;   // [kb][m_cap], NT consecutive rows
+      float sb_n = sb_ptr[0];
+      constexpr int kAhead = 4;   // K blocks ahead for the L1 prefetch of the activation scales
+      if (MODE == 1 && lane * 32 < NT) {
+#pragma unroll 1
+        for (int kb = 0; kb < kAhead && kb < kblocks; ++kb) prefetch_l1(sa_ptr + (size_t)kb * p.m_cap + lane * 32);
+      }
+
+      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        const uint32_t b = it % kRing, bph = (it / kRing) & 1u;
+        // scales of this K block: NT token scales (the same for every thread, an L1 broadcast
+        // thanks to the prefetch) and one weight scale; loaded before the wait so that the
+        // latency hides behind it
+        float4 sa_c[NT / 4];
+        if (MODE == 1) {
+#pragma unroll
+          for (int j = 0; j < NT / 4; ++j)
+            sa_c[j] = reinterpret_cast<const float4*>(sa_ptr + (size_t)kb * p.m_cap)[j];
+          if (kb + kAhead < kblocks && lane * 32 < NT)
+            prefetch_l1(sa_ptr + (size_t)(kb + kAhead) * p.m_cap + lane * 32);
+        }
+        const float sb_cur = sb_n;
+        if (kb + 1 < kblocks) sb_n = sb_ptr[kb + 1];
+        bool ok = mbar_wait(bar_tfull + 8 * b, bph, abort_flag, p.status, 24);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) { alive = false; break; }
+        tc_fence_after();
+        const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + b * NT;
+        if constexpr (NT == 16) {
+          uint32_t r[16];
+          tmem_ld_32x16(t_row, r);
+          tmem_ld_wait_on16(r);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float sc = MODE == 1 ? reinterpret_cast<const float*>(sa_c)[j] * sb_cur : sb_cur;
+            acc[j] = fmaf(__uint_as_float(r[j]), sc, acc[j]);
+          }
+        } else {
+          uint32_t ra[32], rb[32];
+          tmem_ld_32x32(t_row, ra);
+          tmem_ld_32x32(t_row + 32, rb);
+          tmem_ld_wait_on(ra, rb);
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float s0 = MODE == 1 ? reinterpret_cast<const float*>(sa_c)[j] * sb_cur : sb_cur;
+            const float s1 = MODE == 1 ? reinterpret_cast<const float*>(sa_c)[32 + j] * sb_cur : sb_cur;
+            acc[j] = fmaf(__uint_as_float(ra[j]), s0, acc[j]);
+            acc[32 + j] = fmaf(__uint_as_float(rb[j]), s1, acc[32 + j]);
+          }
+        }
+      }
+      if (!alive) break;
+
+      const int cnt = min(p.expert_count[e], NT);   // real rows of this expert
+      if (MODE == 1) {
+        // up warp q (2, 3) hands its u values to gate warp q-2 through shared memory
+        // ([token][row] so that lanes hit consecutive banks); bounded mbarrier waits, no bar.sync.
+        const int pr = q & 1;
+        const uint32_t xph = xi & 1u;
+        if (q >= 2) {
+          bool okx = mbar_wait(bar_xfree + 8 * pr, xph ^ 1u, abort_flag, p.status, 27);
+          okx = __all_sync(0xffffffffu, okx);
+          if (!okx) { alive = false; break; }
+#pragma unroll
+          for (int j = 0; j < NT; ++j) xch[j * 64 + pr * 32 + lane] = acc[j];
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_xready + 8 * pr);
+        } else {
+          bool okx = mbar_wait(bar_xready + 8 * pr, xph, abort_flag, p.status, 28);
+          okx = __all_sync(0xffffffffu, okx);
+          if (!okx) { alive = false; break; }
+          const int col = slab * 64 + q * 32 + lane;         // activation column of this lane
+#pragma unroll
+          for (int j = 0; j < NT; ++j) {
+            if (j < cnt) {
+              const float u = xch[j * 64 + pr * 32 + lane];
+              const __half hv = __float2half_rn(silu_mul_d(acc[j], u));
+              p.act[(size_t)(row0 + j) * p.inter + col] = hv;
+              const uint32_t mx = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(__half2float(hv))));
+              if (lane == 0) atomicMax(p.row_amax + row0 + j, mx);
+            }
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_xfree + 8 * pr);
+        }
+        ++xi;
+      } else {
+        const int col = slab * kSlabRows + q * 32 + lane;    // output column of this lane
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+          if (j < cnt) {
+            const float rs = p.row_scale[row0 + j] * p.row_weight[row0 + j];
+            p.y[(size_t)(row0 + j) * p.hidden + col] = __float2bfloat16_rn(acc[j] * rs);
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+template <int MODE, int NT>
+cudaError_t launch_one(const GemmParams& p, int num_sms, cudaStream_t stream) {
+  decode_gemm_kernel<MODE, NT><<<num_sms, kThreads, DCfg<NT>::kSmemBytes, stream>>>(p);
+  return cudaGetLastError();
+}
+
+template <int MODE, int NT>
+cudaError_t configure_one() {
+  return cudaFuncSetAttribute(decode_gemm_kernel<MODE, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              DCfg<NT>::kSmemBytes);
+}
+
+}  // namespace
+
+cudaError_t configure_decode_gemm() {
+  cudaError_t e;
+  if ((e = configure_one<1, 16>()) != cudaSuccess) return e;
+  if ((e = configure_one<1, 64>()) != cudaSuccess) return e;
+  if ((e = configure_one<2, 16>()) != cudaSuccess) return e;
+  return configure_one<2, 64>();
+}
+
+cudaError_t launch_decode_gemm(int mode, int nt, const GemmParams& p, int num_sms, cudaStream_t stream) {
+  if (mode == 1) return nt == 16 ? launch_one<1, 16>(p, num_sms, stream) : launch_one<1, 64>(p, num_sms, stream);
+  return nt == 16 ? launch_one<2, 16>(p, num_sms, stream) : launch_one<2, 64>(p, num_sms, stream);
+}
+
+}  // namespace b200moe

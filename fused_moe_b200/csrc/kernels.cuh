@@ -1,6 +1,8 @@
 // Launchers of the device kernels (one translation unit each), called from capi.cu.
 #pragma once
 
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace b200moe {
@@ -15,7 +17,7 @@ cudaError_t launch_count(const int32_t* ids, long long row_stride, int T, int lo
 cudaError_t launch_permute(const Workspace& ws, const int32_t* ids, long long ids_stride, const float* w,
                            long long w_stride, const uint8_t* hidden, long long hidden_row_stride,
                            const float* hscale, long long sstride_t, long long sstride_kb, int T, int e_local,
-                           int local_off, int hidden_dim, int num_sms, cudaStream_t stream);
+                           int local_off, int hidden_dim, int pad_rows, int num_sms, cudaStream_t stream);
 
 // Arguments of the two grouped GEMMs.  `tmap_a` covers the packed rows [m_cap][K],
 // `tmap_b` the weights viewed as [e_local * N][K]; both e4m3, 128-byte swizzled boxes.
@@ -25,6 +27,7 @@ struct GemmParams {
   const int* meta;          // [0] = number of 128-row M tiles
   const int* tile_expert;   // expert of each M tile
   const int* row_token;     // token of each packed row, -1 for padding
+  const int* expert_count;  // rows per local expert (decode kernel)
   const float* a_scale;     // GEMM1: [K/128][m_cap] activation scales
   const float* b_scale;     // [e_local][N/128][K/128] weight scales
   int m_cap;
@@ -33,7 +36,7 @@ struct GemmParams {
   int n_tiles;              // N tiles per M tile
   int inter;
   int hidden;
-  float* act;               // GEMM1 out: [m_cap][inter] fp32
+  __half* act;              // GEMM1 out: [m_cap][inter] fp16
   unsigned* row_amax;       // GEMM1 out: bits of max |act| per row
   const float* row_scale;   // GEMM2 in: requantisation scale per row
   const float* row_weight;  // GEMM2 in: routing weight per row
@@ -46,6 +49,14 @@ struct GemmParams {
 // mode 1: GEMM1 + SwiGLU + row amax; mode 2: GEMM2 + weighted combine.  bn: 128 or 256.
 cudaError_t launch_grouped_gemm(int mode, int bn, const GemmParams& p, int num_sms, cudaStream_t stream);
 cudaError_t configure_grouped_gemm();   // opt-in shared memory sizes, once per process and device
+
+// The same GEMMs on CTA pairs (cta_group::2), tile 256 rows x 256 weight rows; segments must be padded to 256 rows.
+cudaError_t launch_grouped_gemm_pair(int mode, const GemmParams& p, int num_sms, cudaStream_t stream);
+cudaError_t configure_grouped_gemm_pair();
+
+// Decode sizes (T <= nt, nt 16 or 64): operands swapped, weights on the MMA's M side (gemm_decode.cu).
+cudaError_t launch_decode_gemm(int mode, int nt, const GemmParams& p, int num_sms, cudaStream_t stream);
+cudaError_t configure_decode_gemm();
 
 cudaError_t launch_requant(const Workspace& ws, int inter, int num_sms, cudaStream_t stream);
 cudaError_t launch_combine(const Workspace& ws, int T, int hidden, void* out_bf16, long long out_row_stride,

@@ -19,7 +19,7 @@ namespace b200moe {
 namespace {
 
 __global__ void __launch_bounds__(256)
-scan_kernel(Workspace ws, int e_local, int n_chunks) {
+scan_kernel(Workspace ws, int e_local, int n_chunks, int pad_rows) {
   __shared__ int s_scan[256];
   const int e = threadIdx.x;
   int* chunk_counts = ws.at<int>(ws.L.chunk_counts);
@@ -31,7 +31,7 @@ scan_kernel(Workspace ws, int e_local, int n_chunks) {
       total += chunk_counts[c * e_local + e];
     }
   }
-  int padded = (total + kTileM - 1) / kTileM * kTileM;
+  int padded = (total + pad_rows - 1) / pad_rows * pad_rows;   // 128, or 256 when CTA pairs run the GEMMs
   s_scan[e] = padded;
   __syncthreads();
   // inclusive Hillis-Steele scan over 256 entries
@@ -65,6 +65,7 @@ scan_kernel(Workspace ws, int e_local, int n_chunks) {
     meta[0] = padded_total / kTileM;
     meta[1] = padded_total;
     meta[2] = s_rows;
+    meta[3] = pad_rows;
   }
 }
 
@@ -146,9 +147,9 @@ gather_kernel(Workspace ws, const uint8_t* __restrict__ hidden, long long hidden
 cudaError_t launch_permute(const Workspace& ws, const int32_t* ids, long long ids_stride, const float* w,
                            long long w_stride, const uint8_t* hidden, long long hidden_row_stride,
                            const float* hscale, long long sstride_t, long long sstride_kb, int T, int e_local,
-                           int local_off, int hidden_dim, int num_sms, cudaStream_t stream) {
+                           int local_off, int hidden_dim, int pad_rows, int num_sms, cudaStream_t stream) {
   const int n_chunks = (T + kChunkTokens - 1) / kChunkTokens;
-  scan_kernel<<<1, 256, 0, stream>>>(ws, e_local, n_chunks);
+  scan_kernel<<<1, 256, 0, stream>>>(ws, e_local, n_chunks, pad_rows);
   cudaError_t err = cudaGetLastError();
   if (err != cudaSuccess) return err;
   if (n_chunks > 0) {

@@ -48,63 +48,64 @@ route_kernel(const void* __restrict__ logits, int logits_dtype, const void* __re
   for (int g = 0; g < kNumGroups; ++g) b[g] = load_as_float(bias, bias_dtype, g * 32 + lane);
 
   for (int t = blockIdx.x * kRouteWarps + warp; t < T; t += gridDim.x * kRouteWarps) {
+    // Every selection is "maximum key, lowest index among equals": one warp-wide integer
+    // max (redux.sync) on the order keys plus a ballot, instead of a shuffle tree.
     float s[kNumGroups];
-    uint32_t key[kNumGroups];   // order key of sigmoid + bias
+    uint32_t key[kNumGroups];   // order key of sigmoid + bias (never 0 for a finite value)
     float gscore = 0.f;         // lane g (< 8) keeps the score of group g
 #pragma unroll
     for (int g = 0; g < kNumGroups; ++g) {
       float x = load_as_float(logits, logits_dtype, (size_t)t * kNumExperts + g * 32 + lane);
       s[g] = sigmoid_round_once(x);
-      float swb = s[g] + b[g];
-      key[g] = order_key(swb);
-      // top-2 with multiplicity: take the best (value, lane) pair, drop that one lane, take the best again
-      unsigned long long mine = ((unsigned long long)key[g] << 32) | (uint32_t)(31 - lane);
-      unsigned long long best = warp_max_u64(mine);
-      unsigned long long rest = warp_max_u64(mine == best ? 0ull : mine);
-      uint32_t k1 = (uint32_t)(best >> 32), k2 = (uint32_t)(rest >> 32);
-      float v1 = __uint_as_float((k1 & 0x80000000u) ? (k1 & 0x7fffffffu) : ~k1);
-      float v2 = __uint_as_float((k2 & 0x80000000u) ? (k2 & 0x7fffffffu) : ~k2);
-      float sc = v1 + v2;
-      if (lane == g) gscore = sc;
+      key[g] = order_key(s[g] + b[g]);
     }
-    // top-4 groups: four rounds of (score, lowest index) maxima over lanes 0..7
-    unsigned long long gk = lane < kNumGroups
-        ? (((unsigned long long)order_key(gscore) << 32) | (uint32_t)(kNumGroups - 1 - lane) | 0x100u)
-        : 0ull;
+#pragma unroll
+    for (int g = 0; g < kNumGroups; ++g) {
+      // top-2 with multiplicity: best key, drop ONE lane that holds it, best key again
+      const uint32_t k1 = __reduce_max_sync(0xffffffffu, key[g]);
+      const uint32_t holders = __ballot_sync(0xffffffffu, key[g] == k1);
+      const int first = __ffs(holders) - 1;
+      const uint32_t k2 = __reduce_max_sync(0xffffffffu, lane == first ? 0u : key[g]);
+      const float v1 = __uint_as_float((k1 & 0x80000000u) ? (k1 & 0x7fffffffu) : ~k1);
+      const float v2 = __uint_as_float((k2 & 0x80000000u) ? (k2 & 0x7fffffffu) : ~k2);
+      if (lane == g) gscore = v1 + v2;
+    }
+    // top-4 groups, lowest group index on ties
+    uint32_t gk = lane < kNumGroups ? order_key(gscore) : 0u;
     uint32_t group_mask = 0;
 #pragma unroll
     for (int r = 0; r < kTopKGroups; ++r) {
-      unsigned long long best = warp_max_u64(gk);
-      int g = kNumGroups - 1 - (int)(best & 0xffu);
+      const uint32_t best = __reduce_max_sync(0xffffffffu, gk);
+      const uint32_t holders = __ballot_sync(0xffffffffu, gk == best && lane < kNumGroups);
+      const int g = __ffs(holders) - 1;
       group_mask |= 1u << g;
-      if (lane == g) gk = 0ull;
+      if (lane == g) gk = 0u;
     }
-    // top-8 experts among the kept groups; a taken or masked candidate has key 0
-    unsigned long long cand[kNumGroups];
+    // top-8 experts among the kept groups, lowest expert id on ties; a taken or masked candidate has key 0
+    uint32_t cand[kNumGroups];
 #pragma unroll
-    for (int g = 0; g < kNumGroups; ++g) {
-      uint32_t id = g * 32 + lane;
-      cand[g] = ((group_mask >> g) & 1u)
-          ? (((unsigned long long)key[g] << 32) | (uint32_t)(kNumExperts - 1 - id) | 0x100u)
-          : 0ull;
-    }
+    for (int g = 0; g < kNumGroups; ++g) cand[g] = ((group_mask >> g) & 1u) ? key[g] : 0u;
     float ssum = 0.f;
     float my_s = 0.f;   // lane k keeps s of the k-th winner
     int my_id = 0;
 #pragma unroll
     for (int k = 0; k < kTopK; ++k) {
-      unsigned long long loc = cand[0];
+      uint32_t loc = cand[0];
 #pragma unroll
       for (int g = 1; g < kNumGroups; ++g) loc = cand[g] > loc ? cand[g] : loc;
-      unsigned long long best = warp_max_u64(loc);
-      int id = kNumExperts - 1 - (int)(best & 0xffu);
-      int wl = id & 31, wg = id >> 5;
+      const uint32_t best = __reduce_max_sync(0xffffffffu, loc);
+      uint32_t mine = 0xffffffffu;   // lowest id this lane holds at the best key
+#pragma unroll
+      for (int g = kNumGroups - 1; g >= 0; --g)
+        if (cand[g] == best) mine = (uint32_t)(g * 32 + lane);
+      const int id = (int)__reduce_min_sync(0xffffffffu, mine);
+      const int wl = id & 31, wg = id >> 5;
       float sw = 0.f;
 #pragma unroll
       for (int g = 0; g < kNumGroups; ++g) {
         if (g == wg) {
           sw = s[g];
-          if (lane == wl) cand[g] = 0ull;
+          if (lane == wl) cand[g] = 0u;
         }
       }
       sw = __shfl_sync(0xffffffffu, sw, wl);

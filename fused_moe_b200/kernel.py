@@ -20,6 +20,7 @@ is in ``libb200moe.so``.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Dict, Optional, Tuple
 
 import torch
@@ -72,6 +73,15 @@ class Workspace:
 
 _workspaces: Dict[Tuple, Workspace] = {}
 
+# CUDA-graph replay of whole layer calls for launch-bound batch sizes.
+GRAPH_MAX_TOKENS = 1024
+GRAPH_CACHE_ENTRIES = 64
+_graph_cache: Dict[Tuple, object] = {}
+
+
+def _graphs_enabled() -> bool:
+    return os.environ.get("B200MOE_DISABLE_GRAPH", "0") in ("", "0")
+
 
 def get_workspace(device: torch.device, T: int, e_local: int, hidden: int, inter: int) -> Workspace:
     key = (device.type, device.index, e_local, hidden, inter)
@@ -80,6 +90,7 @@ def get_workspace(device: torch.device, T: int, e_local: int, hidden: int, inter
         cap = max(T, 1)
         if ws is not None:
             cap = max(cap, 2 * ws.T if ws.T < 4096 else T)
+            _graph_cache.clear()       # captured graphs point into the buffer being replaced
             del _workspaces[key]
             del ws
         ws = Workspace(device, cap, e_local, hidden, inter)
@@ -88,6 +99,7 @@ def get_workspace(device: torch.device, T: int, e_local: int, hidden: int, inter
 
 
 def clear_workspaces() -> None:
+    _graph_cache.clear()
     _workspaces.clear()
 
 
@@ -192,17 +204,44 @@ def custom_kernel(routing_logits, routing_bias, hidden_states, hidden_states_sca
             result = out
         if T == 0:
             return result
-        stream = torch.cuda.current_stream(dev).cuda_stream
         ws.last_T = T
-        rc = _capi.lib().b200moe_run(
-            logits.data_ptr(), _dtype_tag(logits, "routing_logits"),
-            bias.data_ptr(), _dtype_tag(bias, "routing_bias"),
-            hs.data_ptr(), hs.stride(0),
-            hidden_states_scale.data_ptr(), st_t, st_kb,
-            w1.data_ptr(), s1.data_ptr(), w2.data_ptr(), s2.data_ptr(),
-            T, e_local, local_off, rsf, hidden, inter,
-            ws.ptr, ws.nbytes, result.data_ptr(), result.stride(0), stream)
-        _capi.check(rc, "b200moe_run")
+        lt, bt = _dtype_tag(logits, "routing_logits"), _dtype_tag(bias, "routing_bias")
+
+        def launch():
+            rc = _capi.lib().b200moe_run(
+                logits.data_ptr(), lt, bias.data_ptr(), bt, hs.data_ptr(), hs.stride(0),
+                hidden_states_scale.data_ptr(), st_t, st_kb,
+                w1.data_ptr(), s1.data_ptr(), w2.data_ptr(), s2.data_ptr(),
+                T, e_local, local_off, rsf, hidden, inter,
+                ws.ptr, ws.nbytes, result.data_ptr(), result.stride(0),
+                torch.cuda.current_stream(dev).cuda_stream)
+            _capi.check(rc, "b200moe_run")
+
+        if T <= GRAPH_MAX_TOKENS and _graphs_enabled() and not torch.cuda.is_current_stream_capturing():
+            # Small batches are launch-bound: the nine launches of a call are replayed as one CUDA
+            # graph, cached per (shapes, argument addresses) like the reference (kernel.py:613-635).
+            key = (dev.index, T, e_local, hidden, inter, local_off, rsf, lt, bt, logits.data_ptr(),
+                   bias.data_ptr(), hs.data_ptr(), hs.stride(0), hidden_states_scale.data_ptr(), st_t, st_kb,
+                   w1.data_ptr(), s1.data_ptr(), w2.data_ptr(), s2.data_ptr(), ws.ptr, result.data_ptr(),
+                   result.stride(0))
+            entry = _graph_cache.get(key)
+            if entry is None:
+                if len(_graph_cache) >= GRAPH_CACHE_ENTRIES:
+                    _graph_cache.clear()
+                _graph_cache[key] = 1          # first sighting: run eagerly (also does the one-time set-up)
+                launch()
+            elif entry == 1:
+                graph = torch.cuda.CUDAGraph()
+                torch.cuda.synchronize(dev)
+                with torch.cuda.graph(graph):
+                    launch()
+                _graph_cache[key] = graph
+                graph.replay()
+            else:
+                entry.replay()
+        else:
+            launch()
+        stream = torch.cuda.current_stream(dev).cuda_stream
         if check_status:
             code, detail = ws.read_status(stream)
             if code != 0:

@@ -72,7 +72,7 @@ typedef struct b200moe_ws_layout {
   uint64_t row_weight;    /* float[m_cap] */
   uint64_t a_packed;      /* uint8[m_cap][hidden] e4m3 rows in expert order */
   uint64_t a_scale;       /* float[hidden/128][m_cap] */
-  uint64_t act;           /* float[m_cap][inter] SwiGLU output */
+  uint64_t act;           /* fp16[m_cap][inter] SwiGLU output */
   uint64_t row_amax;      /* uint32[m_cap]: bits of max|act| per row */
   uint64_t act_q;         /* uint8[m_cap][inter] e4m3 */
   uint64_t row_scale;     /* float[m_cap] */

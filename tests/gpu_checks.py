@@ -44,9 +44,11 @@ def check_stages(inp_cpu, res, ws, act_rtol=2e-3, verbose=False):
     want_counts = O.local_counts(ora["ids"], off, e_local)
     assert np.array_equal(counts, want_counts), "permute: per-expert counts"
     row0 = ws.view("expert_row0", torch.int32, (e_local + 1,)).cpu().numpy()
-    padded = (want_counts + 127) // 128 * 128
-    assert np.array_equal(row0, np.concatenate([[0], np.cumsum(padded)])), "permute: padded segment starts"
     meta = ws.view("meta", torch.int32, (8,)).cpu().numpy()
+    pad = int(meta[3])                      # 128, or 256 when CTA pairs run the GEMMs
+    assert pad in (128, 256)
+    padded = (want_counts + pad - 1) // pad * pad
+    assert np.array_equal(row0, np.concatenate([[0], np.cumsum(padded)])), "permute: padded segment starts"
     m_pad = int(row0[-1])
     assert meta[0] == m_pad // 128 and meta[1] == m_pad and meta[2] == want_counts.sum(), "permute: meta"
     info.update(m_local=int(want_counts.sum()), n_active=int((want_counts > 0).sum()), m_pad=m_pad)
@@ -58,7 +60,7 @@ def check_stages(inp_cpu, res, ws, act_rtol=2e-3, verbose=False):
     tile_expert = ws.view("tile_expert", torch.int32, (L.max_tiles,))[:m_pad // 128].cpu().numpy()
     a_packed = ws.view("a_packed", torch.uint8, (L.m_cap, hidden))[:m_pad].cpu().numpy()
     a_scale = ws.view("a_scale", torch.float32, (hidden // 128, L.m_cap))[:, :m_pad].cpu().numpy()
-    act = ws.view("act", torch.float32, (L.m_cap, inter))[:m_pad].cpu().numpy()
+    act = ws.view("act", torch.float16, (L.m_cap, inter))[:m_pad].float().cpu().numpy()
     amax_bits = ws.view("row_amax", torch.int32, (L.m_cap,))[:m_pad].cpu().numpy()
     act_q = ws.view("act_q", torch.uint8, (L.m_cap, inter))[:m_pad].cpu().numpy()
     row_scale = ws.view("row_scale", torch.float32, (L.m_cap,))[:m_pad].cpu().numpy()
