@@ -275,12 +275,17 @@ int b200moe_experts(const int32_t* topk_ids, int64_t ids_row_stride, const float
                           use_pairs ? 2 * kTileM : kTileM, num_sms, st));
 
   // small problems get the narrower N tile: more work items to spread over the SMs
-  // Up to 64 tokens: swapped-operand decode kernels (B200MOE_DECODE=0 turns them off).
+  // Up to 16 tokens: swapped-operand decode kernels (B200MOE_DECODE=0 turns them off; B200MOE_DECODE=64
+  // extends them to 64 tokens, where the 128-row tiles currently measure faster).
   static const bool decode_on = [] {
     const char* v = getenv("B200MOE_DECODE");
     return !(v && v[0] == '0');
   }();
-  const int nt = (decode_on && !use_pairs && T <= 64) ? (T <= 16 ? 16 : 64) : 0;
+  static const int decode_max_t = [] {
+    const char* v = getenv("B200MOE_DECODE");
+    return (v && v[0] == '6') ? 64 : 16;
+  }();
+  const int nt = (decode_on && !use_pairs && T <= decode_max_t && hidden <= 7168) ? (T <= 16 ? 16 : 64) : 0;
   const int bn = use_pairs ? 256 : (nt ? 128 : ((long long)T * kTopK <= 2048 ? 128 : 256));
 
   GemmParams g1;

@@ -7,7 +7,7 @@
 //
 // One CTA per SM walks work items (M tile of 128 packed rows, N tile of BN weight rows).
 // Per 128-wide K block (= one fp32 scale block, = one 128-byte swizzled TMA row):
-//   warp 0      TMA producer: A box 128x128 B and two B boxes (BN/2)x128 B into a smem ring
+//   warps 0, 3  TMA producers (one lane each, alternate K blocks): A box 128x128 B and two B boxes (BN/2)x128 B into a smem ring
 //   warps 1, 2  (one lane each, alternate K blocks) issue 4 tcgen05.mma (K=32 each) into one of two TMEM accumulators, starting
 //               from zero, so each accumulator holds the raw e4m3 dot product of one K block
 //   warps 4-11  read that accumulator back (tcgen05.ld, two loads in flight) and fold it into
@@ -125,8 +125,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
 
   if (warp < kCtrlWarps) {
     reg_dealloc<kCtrlRegs>();
-    if (warp == 0 && lane == 0) {
-      // ------------------------------ TMA producer ------------------------------
+    if ((warp == 0 || warp == 3) && lane == 0) {
+      // ------------------------------ TMA producers (alternate K blocks) ------------------------------
+      const uint32_t pme = warp == 0 ? 0u : 1u;
       uint32_t it = 0;
       bool alive = true;
       for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x) {
@@ -141,6 +142,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           brow1 = brow0 + BN / 2;
         }
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          if ((it & 1u) != pme) continue;
           const uint32_t s = it % S, ph = (it / S) & 1u;
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status, 1)) { alive = false; break; }
           const uint32_t full = bar_full + 8 * s;
@@ -154,7 +156,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       // Copies still in flight must land before the CTA's shared memory is released.
       const uint32_t first = it > (uint32_t)S ? it - S : 0u;
       for (uint32_t j = first; j < it; ++j)
-        (void)mbar_wait(bar_full + 8 * (j % S), (j / S) & 1u, abort_flag + 1, p.status, 6);
+        if ((j & 1u) == pme) (void)mbar_wait(bar_full + 8 * (j % S), (j / S) & 1u, abort_flag + 1, p.status, 6);
     } else if ((warp == 1 || warp == 2) && lane == 0) {
       // ------------------------------ MMA issuers ------------------------------
       // Two threads (on different SM sub-partitions) take alternate K blocks.  Issuing the

@@ -26,7 +26,7 @@ namespace b200moe {
 
 namespace {
 
-constexpr int kThreads = 256;            // warps 0-3 control (0: TMA, 1 and 2: MMA), warps 4-7 promotion
+constexpr int kThreads = 256;            // warps 0-3 control (0 and 3: TMA, 1 and 2: MMA), warps 4-7 promotion
 constexpr int kSlabRows = 128;
 constexpr int kWBytes = kSlabRows * kBlockK;   // 16 KiB of weights per stage
 constexpr int kRing = 4;                 // accumulators in tensor memory
@@ -34,10 +34,12 @@ constexpr int kRing = 4;                 // accumulators in tensor memory
 template <int NT> struct DCfg {
   static constexpr int kTokBytes = NT * kBlockK;
   static constexpr int kStageBytes = kWBytes + kTokBytes;
-  static constexpr int kStages = (NT <= 16) ? 10 : 8;
+  static constexpr int kStages = (NT <= 16) ? 9 : 6;
   static constexpr int kTmemCols = (kRing * NT < 32) ? 32 : kRing * NT;
   static constexpr int kXchBytes = 64 * NT * 4;                 // u values of 64 up rows
-  static constexpr int kSmemBytes = kStages * kStageBytes + kXchBytes + 512 + 1024;
+  static constexpr int kMaxKBlocks = 56;                        // hidden <= 7168 for the scale panels
+  static constexpr int kPanelBytes = kMaxKBlocks * NT * 4 + 256;   // one promotion warp's copy of the token scales + weight scales
+  static constexpr int kSmemBytes = kStages * kStageBytes + kXchBytes + 4 * kPanelBytes + 512 + 1024;
 };
 
 __device__ __forceinline__ float silu_mul_d(float g, float u) {
@@ -68,7 +70,8 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t smem_base = smem_u32(smem);
   float* xch = reinterpret_cast<float*>(smem + S * Cfg::kStageBytes);               // [64][NT]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes + Cfg::kXchBytes);
+  float* panels = reinterpret_cast<float*>(smem + S * Cfg::kStageBytes + Cfg::kXchBytes);   // [4 warps][kblocks][NT]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes + Cfg::kXchBytes + 4 * Cfg::kPanelBytes);
   const uint32_t bar_full = smem_u32(bars);
   const uint32_t bar_empty = bar_full + 8 * S;
   const uint32_t bar_tfull = bar_empty + 8 * S;
@@ -116,9 +119,10 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
   const int total_items = m_tiles * p.n_tiles;
   const int kblocks = p.kblocks;
 
-  if (warp == 0) {
+  if (warp == 0 || warp == 3) {
     if (lane == 0) {
-      // ------------------------------ TMA producer ------------------------------
+      // ------------------------------ TMA producers (alternate K blocks) ------------------------------
+      const uint32_t pme = warp == 0 ? 0u : 1u;
       uint32_t it = 0;
       bool alive = true;
       for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x) {
@@ -133,6 +137,7 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
           wrow1 = wrow0 + 64;
         }
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
+          if ((it & 1u) != pme) continue;
           const uint32_t s = it % S, ph = (it / S) & 1u;
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status, 21)) { alive = false; break; }
           const uint32_t full = bar_full + 8 * s;
@@ -145,7 +150,7 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
       }
       const uint32_t first = it > (uint32_t)S ? it - S : 0u;
       for (uint32_t j = first; j < it; ++j)
-        (void)mbar_wait(bar_full + 8 * (j % S), (j / S) & 1u, abort_flag + 1, p.status, 26);
+        if ((j & 1u) == pme) (void)mbar_wait(bar_full + 8 * (j % S), (j / S) & 1u, abort_flag + 1, p.status, 26);
     }
   } else if (warp == 1 || warp == 2) {
     if (lane == 0) {
@@ -192,28 +197,29 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
       else wblock = slab;
       const float* sb_ptr = p.b_scale + ((size_t)e * nblk_per_expert + wblock) * kblocks;
       const float* sa_ptr = MODE == 1 ? p.a_scale + row0 : nullptr;   // [kb][m_cap], NT consecutive rows
-      float sb_n = sb_ptr[0];
-      constexpr int kAhead = 4;   // K blocks ahead for the L1 prefetch of the activation scales
-      if (MODE == 1 && lane * 32 < NT) {
-#pragma unroll 1
-        for (int kb = 0; kb < kAhead && kb < kblocks; ++kb) prefetch_l1(sa_ptr + (size_t)kb * p.m_cap + lane * 32);
+      // GEMM1: the token scales of the whole item ([kblocks][NT] floats) are copied once into
+      // this warp's own panel in shared memory; per K block they are then a broadcast read
+      // instead of a global load whose latency would bound every iteration.
+      float* panel = panels + (size_t)(warp - 4) * (Cfg::kPanelBytes / 4);
+      float* panel_sb = panel + Cfg::kMaxKBlocks * NT;     // this warp's weight scales, one per K block
+      __syncwarp();
+      for (int i = lane; i < kblocks; i += 32) panel_sb[i] = sb_ptr[i];
+      if (MODE == 1) {
+        for (int i = lane; i < kblocks * (NT / 4); i += 32) {
+          const int kb = i / (NT / 4), v = i % (NT / 4);
+          reinterpret_cast<float4*>(panel)[i] = reinterpret_cast<const float4*>(sa_ptr + (size_t)kb * p.m_cap)[v];
+        }
       }
+      __syncwarp();
 
       for (int kb = 0; kb < kblocks; ++kb, ++it) {
         const uint32_t b = it % kRing, bph = (it / kRing) & 1u;
-        // scales of this K block: NT token scales (the same for every thread, an L1 broadcast
-        // thanks to the prefetch) and one weight scale; loaded before the wait so that the
-        // latency hides behind it
         float4 sa_c[NT / 4];
         if (MODE == 1) {
 #pragma unroll
-          for (int j = 0; j < NT / 4; ++j)
-            sa_c[j] = reinterpret_cast<const float4*>(sa_ptr + (size_t)kb * p.m_cap)[j];
-          if (kb + kAhead < kblocks && lane * 32 < NT)
-            prefetch_l1(sa_ptr + (size_t)(kb + kAhead) * p.m_cap + lane * 32);
+          for (int j = 0; j < NT / 4; ++j) sa_c[j] = reinterpret_cast<const float4*>(panel + kb * NT)[j];
         }
-        const float sb_cur = sb_n;
-        if (kb + 1 < kblocks) sb_n = sb_ptr[kb + 1];
+        const float sb_cur = panel_sb[kb];
         bool ok = mbar_wait(bar_tfull + 8 * b, bph, abort_flag, p.status, 24);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { alive = false; break; }
