@@ -56,6 +56,7 @@ SIGNATURES = {
                          _I, _I, _I, _F, _I, _I, _P, _Z, _P, _L, _P]),
     "b200moe_read_status": (_I, [_P, _P, C.POINTER(C.c_int32)]),
     "b200moe_profile_next_gemm1": (_I, [_P, _P]),
+    "b200moe_selftest_wait_timeout": (_I, [_P, _P]),
     "b200moe_launches_per_run": (_I, [_I, _I]),
     "b200moe_ep_pack": (_I, [_P, _P, _P, _L, _P, _L, _L, _I, _I, _I, _P, _P, _P, _P]),
     "b200moe_ep_combine": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),

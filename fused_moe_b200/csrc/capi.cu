@@ -389,6 +389,14 @@ int b200moe_read_status(const void* workspace, void* stream, int32_t* detail) {
   return host[kStatusCode];
 }
 
+int b200moe_selftest_wait_timeout(void* status_int4, void* stream) {
+  if (!status_int4) return B200MOE_ERR_INVALID_ARGUMENT;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  CUDA_TRY(cudaMemsetAsync(status_int4, 0, 16, st));
+  CUDA_TRY(launch_wait_timeout_selftest(reinterpret_cast<int*>(status_int4), st));
+  return B200MOE_OK;
+}
+
 int b200moe_ep_pack(const int32_t* topk_ids, const float* topk_w, const uint8_t* hidden_states,
                     int64_t hidden_row_stride, const float* hidden_scale, int64_t scale_stride_t,
                     int64_t scale_stride_kb, int T, int hidden, int world, uint8_t* send_rows, int32_t* dest_counts,

@@ -84,8 +84,8 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // Bounded wait on an mbarrier phase.  Returns false when the CTA is aborting (another
 // thread gave up) or when this wait ran out of budget; in the latter case the status word
 // in global memory receives the timeout code and `where` for diagnosis.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int where) {
+__device__ __forceinline__ bool mbar_wait_budget(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                 int* status, int where, long long budget_cycles) {
   long long t0 = 0;
   uint32_t spins = 0;
   while (true) {
@@ -96,7 +96,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       long long now = clock64();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitBudgetCycles) {
+      } else if (now - t0 > budget_cycles) {
         *abort_flag = 1;
         if (atomicCAS(status + kStatusCode, 0, (int)B200MOE_ERR_DEVICE_TIMEOUT) == 0)
           status[kStatusDetail] = where;
@@ -104,6 +104,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* status, int where) {
+  return mbar_wait_budget(bar, parity, abort_flag, status, where, kWaitBudgetCycles);
 }
 
 // TMA: 2D tiled load global -> shared, completion counted on an mbarrier.
@@ -354,6 +358,13 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar, uint16_t cta_mask) 
 }
 __device__ __forceinline__ void tc_commit_pair_local(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// 32-byte store (one full sector per lane); address must be 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(void* addr, const uint32_t (&v)[8]) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+               ::"l"(addr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+               : "memory");
 }
 
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {

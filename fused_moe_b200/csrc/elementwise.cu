@@ -104,7 +104,30 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ tok_
   }
 }
 
+// Self-test of the bounded wait: one thread waits on a barrier that nothing ever arrives on,
+// with a budget of about a millisecond, and must come back with the timeout code recorded.
+__global__ void wait_timeout_selftest_kernel(int* status) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0;
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const bool ok = mbar_wait_budget(smem_u32(&bar), 0u, &abort_flag, status, 99, 2000000LL);
+    status[2] = ok ? 1 : 0;
+    status[3] = abort_flag;
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_wait_timeout_selftest(int* status, cudaStream_t stream) {
+  wait_timeout_selftest_kernel<<<1, 32, 0, stream>>>(status);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_requant(const Workspace& ws, int inter, int num_sms, cudaStream_t stream) {
   long long cap_rows = ws.L.m_cap;

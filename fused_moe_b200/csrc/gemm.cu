@@ -324,35 +324,31 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           __half* dst = p.act + (size_t)row * p.inter + n_tile * (BN / 2) + h * (BN / 4);
           float amax = 0.f;
 #pragma unroll
-          for (int j = 0; j < HP; j += 4) {
-            uint4 pk;
-            uint32_t* w = reinterpret_cast<uint32_t*>(&pk);
+          for (int j = 0; j < HP; j += 8) {
+            uint32_t w[8];
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
+            for (int t = 0; t < 8; ++t) {
               __half2 hh = __floats2half2_rn(silu_mul(acc[j + t].x, acc[HP + j + t].x),
                                              silu_mul(acc[j + t].y, acc[HP + j + t].y));
               float2 back = __half22float2(hh);
               amax = fmaxf(amax, fmaxf(fabsf(back.x), fabsf(back.y)));
               w[t] = *reinterpret_cast<uint32_t*>(&hh);
             }
-            *reinterpret_cast<uint4*>(dst + 2 * j) = pk;
+            st_global_v8(dst + 2 * j, w);
           }
           atomicMax(p.row_amax + row, __float_as_uint(amax));
         } else {
           const float rs = p.row_scale[row] * p.row_weight[row];
           __nv_bfloat16* dst = p.y + (size_t)row * p.hidden + n_tile * BN + h * (BN / 2);
 #pragma unroll
-          for (int j = 0; j < CPT / 2; j += 4) {
-            uint4 pk;
-            __nv_bfloat162 t0 = __floats2bfloat162_rn(acc[j].x * rs, acc[j].y * rs);
-            __nv_bfloat162 t1 = __floats2bfloat162_rn(acc[j + 1].x * rs, acc[j + 1].y * rs);
-            __nv_bfloat162 t2 = __floats2bfloat162_rn(acc[j + 2].x * rs, acc[j + 2].y * rs);
-            __nv_bfloat162 t3 = __floats2bfloat162_rn(acc[j + 3].x * rs, acc[j + 3].y * rs);
-            pk.x = *reinterpret_cast<uint32_t*>(&t0);
-            pk.y = *reinterpret_cast<uint32_t*>(&t1);
-            pk.z = *reinterpret_cast<uint32_t*>(&t2);
-            pk.w = *reinterpret_cast<uint32_t*>(&t3);
-            *reinterpret_cast<uint4*>(dst + 2 * j) = pk;
+          for (int j = 0; j < CPT / 2; j += 8) {
+            uint32_t w[8];
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+              __nv_bfloat162 v = __floats2bfloat162_rn(acc[j + t].x * rs, acc[j + t].y * rs);
+              w[t] = *reinterpret_cast<uint32_t*>(&v);
+            }
+            st_global_v8(dst + 2 * j, w);
           }
         }
       }

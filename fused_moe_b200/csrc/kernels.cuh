@@ -58,6 +58,8 @@ cudaError_t configure_grouped_gemm_pair();
 cudaError_t launch_decode_gemm(int mode, int nt, const GemmParams& p, int num_sms, cudaStream_t stream);
 cudaError_t configure_decode_gemm();
 
+cudaError_t launch_wait_timeout_selftest(int* status, cudaStream_t stream);
+
 cudaError_t launch_requant(const Workspace& ws, int inter, int num_sms, cudaStream_t stream);
 cudaError_t launch_combine(const Workspace& ws, int T, int hidden, void* out_bf16, long long out_row_stride,
                            int num_sms, cudaStream_t stream);

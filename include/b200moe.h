@@ -184,6 +184,13 @@ B200MOE_API int b200moe_read_status(const void* workspace, void* stream, int32_t
  * `stop_event` after its GEMM1 launch (cudaEvent_t as void*, either may be NULL), once. */
 B200MOE_API int b200moe_profile_next_gemm1(void* start_event, void* stop_event);
 
+/* Failure-detection self-test (the reference has no device-side waits of its own; its
+ * errors are CUTLASS status checks, moe_gemm.cu:296-306): launches a one-block kernel whose
+ * thread waits ~1 ms on a barrier that nothing signals.  status_int4 (device, int32[4],
+ * cleared first) receives [0] = B200MOE_ERR_DEVICE_TIMEOUT, [1] = 99 (where), [2] = 0 (the
+ * wait returned false), [3] = 1 (abort flag set).  The context stays usable. */
+B200MOE_API int b200moe_selftest_wait_timeout(void* status_int4, void* stream);
+
 /* Number of kernels b200moe_run launches for this problem (memsets not counted). */
 B200MOE_API int b200moe_launches_per_run(int T, int e_local);
 

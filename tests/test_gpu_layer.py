@@ -145,3 +145,30 @@ def test_routing_ids_bit_exact_on_every_benchmark_token_count():
         assert np.array_equal(ids.cpu().numpy().astype(np.uint8), g[key + "_ids"]), f"{key}: ids differ"
         if key + "_w" in g.files:
             np.testing.assert_allclose(w.cpu().numpy(), g[key + "_w"], rtol=1e-6, atol=0)
+
+
+def test_signed_scales_as_in_contest_data():
+    """Block scales are applied as signed fp32 multipliers (contest weights carry negative ones)."""
+    g, inp = golden_inputs("layer_small_T200_off64")
+    gen = torch.Generator().manual_seed(9)
+    flip = lambda t: t * (torch.randint(0, 2, t.shape, generator=gen).float() * 2 - 1)
+    inp.gemm1_weights_scale = flip(inp.gemm1_weights_scale)
+    inp.gemm2_weights_scale = flip(inp.gemm2_weights_scale)
+    inp.hidden_states_scale = flip(inp.hidden_states_scale)
+    res, ws = gpu_checks.run_gpu(inp)
+    info = gpu_checks.check_stages(inp, res, ws)
+    assert info["frac_all"] >= 0.999
+
+
+def test_bounded_wait_reports_timeout_and_leaves_the_context_usable():
+    from fused_moe_b200 import _capi
+    dev = torch.device("cuda", 0)
+    st = torch.full((4,), 7, dtype=torch.int32, device=dev)
+    rc = _capi.lib().b200moe_selftest_wait_timeout(st.data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert st.cpu().tolist() == [-5, 99, 0, 1]
+    # the same context still runs the layer
+    g, inp = golden_inputs("layer_small_T64_off0")
+    res, ws = gpu_checks.run_gpu(inp)
+    assert gpu_checks.check_stages(inp, res, ws)["frac_all"] >= 0.999
