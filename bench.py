@@ -10,7 +10,8 @@ step is one layer call on every rank.  `value` = tokens of all ranks per second,
 timed (CUDA events, barrier + synchronize on both sides, max over ranks) with the step's
 inputs already in HBM.  `e2e` = the same through the host entry point with the step's
 tokens in pinned host memory and the bf16 result copied back, inside the timed region
-(expert weights are model state and stay resident).
+(expert weights are model state and stay resident); uploads and downloads of neighbouring
+steps overlap the kernels of the current one (two slots, two copy streams).
 
 Extra objects on the line: `roofline` (GEMM1, the dominant kernel, timed in place with
 CUDA events through b200moe_profile_next_gemm1), `cpu_baseline` (the numpy oracle on the
@@ -305,21 +306,47 @@ def run_b200_arm(args):
     g1_avg_ms = statistics.mean(g1_ms)
 
     # ---- end to end: pinned host inputs in, bf16 result out, every step
-    out_host = torch.empty((TOKENS_PER_RANK, HIDDEN), dtype=torch.bfloat16).pin_memory()
-    d_in = [torch.empty_like(t, device=dev) for t in host]
+    # Two slots of device inputs / outputs and two copy streams: step i+1's upload and step
+    # i-1's download run under step i's kernels, as a serving loop would pipeline them.  Every
+    # step still uploads its own inputs from pinned memory and downloads its own result.
+    out_host = [torch.empty((TOKENS_PER_RANK, HIDDEN), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+    d_in = [[torch.empty_like(t, device=dev) for t in host] for _ in range(2)]
+    d_out = [torch.empty((TOKENS_PER_RANK, HIDDEN), dtype=torch.bfloat16, device=dev) for _ in range(2)]
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    cur = torch.cuda.current_stream(dev)
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_done = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
+    for e in ev_done + ev_out:
+        e.record(cur)
 
-    def e2e_step():
-        for d, h in zip(d_in, host):
-            d.copy_(h, non_blocking=True)
-        o = step(d_in[0], d_in[1].view(torch.float8_e4m3fn), d_in[2])
-        out_host.copy_(o, non_blocking=True)
+    def e2e_step(i):
+        k = i & 1
+        s_in.wait_event(ev_done[k])                 # the kernels that read this input slot are done
+        with torch.cuda.stream(s_in):
+            for d, h in zip(d_in[k], host):
+                d.copy_(h, non_blocking=True)
+            ev_in[k].record(s_in)
+        cur.wait_event(ev_in[k])
+        cur.wait_event(ev_out[k])                   # the download that read this output slot is done
+        if ep is not None:
+            o = step(d_in[k][0], d_in[k][1].view(torch.float8_e4m3fn), d_in[k][2])
+            o.record_stream(s_out)
+        else:
+            o = kernel.custom_kernel(d_in[k][0], bias, d_in[k][1].view(torch.float8_e4m3fn), d_in[k][2],
+                                     w1, s1, w2, s2, 0, RSF, out=d_out[k])
+        ev_done[k].record(cur)
+        s_out.wait_event(ev_done[k])
+        with torch.cuda.stream(s_out):
+            out_host[k].copy_(o, non_blocking=True)
+            ev_out[k].record(s_out)
 
-    for _ in range(3):
-        e2e_step()
+    for i in range(4):
+        e2e_step(i)
     barrier()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
-        e2e_step()
+    for i in range(args.steps):
+        e2e_step(i)
     barrier()
     e2e_s = time.perf_counter() - t0
     # clock samples from the start of the device-timed region to the end of the end-to-end loop
@@ -371,7 +398,7 @@ def run_b200_arm(args):
         return
 
     h2d = sum(t.numel() * t.element_size() for t in host)
-    d2h = out_host.numel() * out_host.element_size()
+    d2h = out_host[0].numel() * out_host[0].element_size()
     launches_per_step = kernel.launches_per_run(TOKENS_PER_RANK, e_local) if world == 1 else 12
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
