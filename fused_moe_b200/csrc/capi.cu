@@ -101,6 +101,11 @@ int make_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64_t k, uin
   return B200MOE_OK;
 }
 
+// (token, k) pairs up to which the 128-wide N tile is used.  Measured on the 32-expert slice at 32..1024
+// tokens the 256-wide tile is as fast or faster everywhere but at 128 tokens (-6 %), so the narrow tile
+// is only reachable through B200MOE_BN=128.
+constexpr long long kSmallTileMaxPairs = 0;
+
 uint64_t align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
 
 int shape_ok(int T, int e_local, int hidden, int inter) {
@@ -286,7 +291,12 @@ int b200moe_experts(const int32_t* topk_ids, int64_t ids_row_stride, const float
     return (v && v[0] == '6') ? 64 : 16;
   }();
   const int nt = (decode_on && !use_pairs && T <= decode_max_t && hidden <= 7168) ? (T <= 16 ? 16 : 64) : 0;
-  const int bn = use_pairs ? 256 : (nt ? 128 : ((long long)T * kTopK <= 2048 ? 128 : 256));
+  static const int bn_forced = [] {
+    const char* v = getenv("B200MOE_BN");
+    return v ? atoi(v) : 0;
+  }();
+  int bn = use_pairs ? 256 : (nt ? 128 : ((long long)T * kTopK <= kSmallTileMaxPairs ? 128 : 256));
+  if (!use_pairs && !nt && (bn_forced == 128 || bn_forced == 256)) bn = bn_forced;
 
   GemmParams g1;
   memset(&g1, 0, sizeof(g1));

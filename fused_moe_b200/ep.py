@@ -145,8 +145,9 @@ class ExpertParallelMoE:
         # counts: what I send to d  <->  what d will receive from me
         recv_counts = torch.empty_like(dest_counts)
         dist.all_to_all_single(recv_counts, dest_counts, group=self.group)
-        send_n = [int(x) for x in dest_counts.cpu().tolist()]
-        recv_n = [int(x) for x in recv_counts.cpu().tolist()]
+        both = torch.stack([dest_counts, recv_counts]).cpu().tolist()    # one host read for both
+        send_n = [int(x) for x in both[0]]
+        recv_n = [int(x) for x in both[1]]
         self.last_send_counts = send_n
         n_recv, n_send = sum(recv_n), sum(send_n)
         self.last_recv_rows = n_recv
