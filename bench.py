@@ -497,10 +497,12 @@ def run_profile_case(args):
                  "mma_wait_epilogue", "mma_wait_tma")
         prof = {"gemm1": dict(zip(names, (int(x) for x in raw[4:13]))),
                 "gemm2": dict(zip(names, (int(x) for x in raw[17:26])))}
-        tr = ws.view("trace", torch.int64, (2, 64, 4)).cpu().numpy()
+        # eight cycle stamps per K block of CTA 0: issuer wait start, operands landed, accumulator free,
+        # MMAs issued; promotion warp 0: accumulator ready, first chunks read, accumulator released, done
+        tr = ws.view("trace", torch.int64, (2, 64, 8)).cpu().numpy()
         for name, t in (("gemm1", tr[0]), ("gemm2", tr[1])):
             base = int(t[8, 0])
-            prof[name]["trace_kb8_23"] = [[int(x) - base for x in t[i]] for i in range(8, 24)]
+            prof[name]["trace_kb8_31"] = [[int(x) - base for x in t[i]] for i in range(8, 32)]
     print(json.dumps({"profile_case": "slice32", "tokens": args.tokens, "zipf": args.zipf, "status": code,
                       "cycle_counters_cta0": prof,
                       "ms_per_call": a.elapsed_time(b) / max(args.steps, 1), "rows": int(meta[2]),

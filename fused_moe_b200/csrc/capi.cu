@@ -147,7 +147,7 @@ void compute_layout(int T, int e_local, int hidden, int inter, b200moe_ws_layout
   L->tok_rows = take((uint64_t)(T > 0 ? T : 1) * kTopK * 4);
   L->topk_ids = take((uint64_t)(T > 0 ? T : 1) * kTopK * 4);
   L->topk_w = take((uint64_t)(T > 0 ? T : 1) * kTopK * 4);
-  L->trace = take(2 * 4 * 64 * 8);   // B200MOE_PROF: absolute cycle stamps of CTA 0's first 64 K blocks
+  L->trace = take(2 * 8 * 64 * 8);   // B200MOE_PROF: absolute cycle stamps of CTA 0's first 64 K blocks
   L->total_bytes = off;
 }
 
@@ -360,7 +360,7 @@ int b200moe_experts(const int32_t* topk_ids, int64_t ids_row_stride, const float
   g2.y = ws.at<__nv_bfloat16>(ws.L.y);
   g2.status = g1.status;
   g2.prof = prof_on ? ws.at<unsigned long long>(ws.L.meta + 136) : nullptr;
-  g2.trace = prof_on ? ws.at<unsigned long long>(ws.L.trace) + 4 * 64 : nullptr;
+  g2.trace = prof_on ? ws.at<unsigned long long>(ws.L.trace) + 8 * 64 : nullptr;
   if (nt) CUDA_TRY(launch_decode_gemm(2, nt, g2, num_sms, st));
   else if (use_pairs) CUDA_TRY(launch_grouped_gemm_pair(2, g2, num_sms, st));
   else CUDA_TRY(launch_grouped_gemm(2, bn, g2, num_sms, st));

@@ -6,6 +6,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <utility>
 
 #include "../../include/b200moe.h"
 
@@ -81,6 +83,20 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return done;
 }
 
+// Non-blocking probe of an mbarrier phase (try_wait may suspend the thread for a while, and
+// waking it again adds latency to a hand-off that sits on the critical path).
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done;
+}
+
 // Bounded wait on an mbarrier phase.  Returns false when the CTA is aborting (another
 // thread gave up) or when this wait ran out of budget; in the latter case the status word
 // in global memory receives the timeout code and `where` for diagnosis.
@@ -108,6 +124,29 @@ __device__ __forceinline__ bool mbar_wait_budget(uint32_t bar, uint32_t parity, 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int where) {
   return mbar_wait_budget(bar, parity, abort_flag, status, where, kWaitBudgetCycles);
+}
+// Same contract, polling with test_wait: for the few waits whose wake-up latency is on the
+// critical path of the MMA / promotion hand-off.
+__device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                               int* status, int where) {
+  long long t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    if (mbar_test_wait(bar, parity)) return true;
+    if (++spins >= 256u) {
+      spins = 0;
+      if (*abort_flag) return false;
+      long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitBudgetCycles) {
+        *abort_flag = 1;
+        if (atomicCAS(status + kStatusCode, 0, (int)B200MOE_ERR_DEVICE_TIMEOUT) == 0)
+          status[kStatusDetail] = where;
+        return false;
+      }
+    }
+  }
 }
 
 // TMA: 2D tiled load global -> shared, completion counted on an mbarrier.
@@ -374,6 +413,42 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
 __device__ __forceinline__ float load_as_float(const void* p, int dtype, size_t i) {
   return dtype == B200MOE_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i])
                                : reinterpret_cast<const float*>(p)[i];
+}
+
+// ---- programmatic dependent launch ----
+// A kernel launched with `launch_chained` may become resident while the kernel before it on
+// the stream is still running, so that its prologue (barrier init, tensor-memory allocation,
+// descriptor fetch) overlaps that kernel's tail.  It must call chain_wait() before it reads
+// or writes anything in global memory: the call returns once the previous kernel has
+// completed and its writes are visible.  chain_release() lets the NEXT kernel on the stream
+// become resident; every kernel calls it right after its own wait, so completion still
+// propagates down the chain in order.  Both are no-ops for a plain launch.
+__device__ __forceinline__ void chain_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void chain_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// B200MOE_PDL=0 falls back to plain stream order.
+inline bool chained_launch_enabled() {
+  static const bool on = [] {
+    const char* v = getenv("B200MOE_PDL");
+    return !(v && v[0] == '0');
+  }();
+  return on;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_chained(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                  Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = chained_launch_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
 }
 
 }  // namespace b200moe

@@ -27,6 +27,8 @@ __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float 
 // be a chain of dependent global loads; 256 threads fetch it in one or two rounds.
 __global__ void __launch_bounds__(256)
 requant_kernel(Workspace ws, int inter) {
+  chain_wait();
+  chain_release();
   const int rows = ws.at<int>(ws.L.meta)[1];
   const int* row_token = ws.at<int>(ws.L.row_token);
   const __half* act = ws.at<__half>(ws.L.act);
@@ -60,6 +62,8 @@ requant_kernel(Workspace ws, int inter) {
 __global__ void __launch_bounds__(256)
 combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ tok_rows, int T, int hidden,
                __nv_bfloat16* __restrict__ out, long long stride) {
+  chain_wait();
+  chain_release();
   const int vec_per_row = hidden / 8;   // 8 bf16 = 16 bytes
   const long long n = (long long)T * vec_per_row;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
@@ -132,8 +136,7 @@ cudaError_t launch_wait_timeout_selftest(int* status, cudaStream_t stream) {
 cudaError_t launch_requant(const Workspace& ws, int inter, int num_sms, cudaStream_t stream) {
   long long cap_rows = ws.L.m_cap;
   int blocks = (int)(cap_rows < (long long)num_sms * 16 ? cap_rows : (long long)num_sms * 16);
-  requant_kernel<<<blocks, 256, 0, stream>>>(ws, inter);
-  return cudaGetLastError();
+  return launch_chained(requant_kernel, dim3(blocks), dim3(256), 0, stream, ws, inter);
 }
 
 cudaError_t launch_combine(const Workspace& ws, int T, int hidden, void* out_bf16, long long out_row_stride,
@@ -143,9 +146,9 @@ cudaError_t launch_combine(const Workspace& ws, int T, int hidden, void* out_bf1
   int blocks = (int)((n + 255) / 256);
   int cap = num_sms * 16;
   if (blocks > cap) blocks = cap;
-  combine_kernel<<<blocks, 256, 0, stream>>>(ws.at<__nv_bfloat16>(ws.L.y), ws.at<int>(ws.L.tok_rows), T, hidden,
-                                             reinterpret_cast<__nv_bfloat16*>(out_bf16), out_row_stride);
-  return cudaGetLastError();
+  return launch_chained(combine_kernel, dim3(blocks), dim3(256), 0, stream,
+                        (const __nv_bfloat16*)ws.at<__nv_bfloat16>(ws.L.y), (const int*)ws.at<int>(ws.L.tok_rows), T,
+                        hidden, reinterpret_cast<__nv_bfloat16*>(out_bf16), out_row_stride);
 }
 
 }  // namespace b200moe

@@ -119,6 +119,10 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Everything above touched only this CTA's own state; global memory written by earlier
+  // kernels is read from here on.
+  chain_wait();
+  chain_release();
   const int m_tiles = p.meta[0];
   const int total_items = m_tiles * p.n_tiles;
   const int kblocks = p.kblocks;
@@ -174,9 +178,11 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           const uint32_t s = it % S, ph = (it / S) & 1u;
           const uint32_t b = me, bph = (it >> 1) & 1u;
           const long long m0 = PROF ? clock64() : 0;
-          if (!mbar_wait(bar_tempty + 8 * b, bph ^ 1u, abort_flag, p.status, 2)) { alive = false; break; }
-          const long long m1 = PROF ? clock64() : 0;
+          // Operands first: they usually landed long ago, so only one wake-up (the free
+          // accumulator) is left on the critical path.
           if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 3)) { alive = false; break; }
+          const long long m1 = PROF ? clock64() : 0;
+          if (!mbar_wait(bar_tempty + 8 * b, bph ^ 1u, abort_flag, p.status, 2)) { alive = false; break; }
           const long long m2 = PROF ? clock64() : 0;
           tc_fence_after();
           const uint32_t a_addr = smem_base + s * Cfg::kStageBytes;
@@ -185,9 +191,16 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           tc_commit(bar_empty + 8 * s);
           tc_commit(bar_tfull + 8 * b);
           if (PROF) {
-            wait_epi += m1 - m0;
-            wait_tma += m2 - m1;
-            t_issue += clock64() - m2;
+            const long long m3 = clock64();
+            wait_tma += m1 - m0;
+            wait_epi += m2 - m1;
+            t_issue += m3 - m2;
+            if (p.trace && blockIdx.x == 0 && it < 64) {
+              p.trace[it * 8 + 0] = (unsigned long long)m0;   // issuer starts waiting for operands
+              p.trace[it * 8 + 1] = (unsigned long long)m1;   // operands landed seen
+              p.trace[it * 8 + 2] = (unsigned long long)m2;   // accumulator free seen
+              p.trace[it * 8 + 3] = (unsigned long long)m3;   // MMAs and commits issued
+            }
           }
         }
       }
@@ -282,8 +295,10 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         tmem_ld_32x32(t_row + chunk_col<MODE, BN>(0, h), ra);
         tmem_ld_32x32(t_row + chunk_col<MODE, BN>(1, h), rb);
         tmem_ld_wait_on(ra, rb);
+        const long long c1a = PROF ? clock64() : 0;
         // The accumulator is free as soon as its last column sits in registers: signal the MMA
         // thread before the remaining FMAs, which then overlap the next K block's MMAs.
+        long long c1b = c1a;
         if constexpr (CH == 2) {
           tc_fence_before();
           __syncwarp();
@@ -296,6 +311,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           fma_chunk(acc + 16, rb, sc0);
           tmem_ld_32x32(t_row + chunk_col<MODE, BN>(3, h), rb);
           tmem_ld_wait_on(ra, rb);
+          c1b = PROF ? clock64() : 0;
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
@@ -307,8 +323,10 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           t_wait += c1 - c0;
           t_promote += c2 - c1;
           if (prof_me && p.trace && it < 64) {
-            p.trace[it * 4 + 2] = (unsigned long long)c1;   // accumulator ready seen by a promotion warp
-            p.trace[it * 4 + 3] = (unsigned long long)c2;   // promotion of this K block done
+            p.trace[it * 8 + 4] = (unsigned long long)c1;    // accumulator ready seen by promotion warp 0
+            p.trace[it * 8 + 5] = (unsigned long long)c1a;   // first two chunks in registers
+            p.trace[it * 8 + 6] = (unsigned long long)c1b;   // last chunk in registers: accumulator released
+            p.trace[it * 8 + 7] = (unsigned long long)c2;    // promotion of this K block done
           }
         }
       }
@@ -371,10 +389,11 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
 template <int MODE, int BN>
 cudaError_t launch_one(const GemmParams& p, int num_sms, cudaStream_t stream) {
   if (p.prof)
-    grouped_gemm_kernel<MODE, BN, true><<<num_sms, kGemmThreads, TileCfg<BN>::kSmemBytes, stream>>>(p);
+    return launch_chained(grouped_gemm_kernel<MODE, BN, true>, dim3(num_sms), dim3(kGemmThreads),
+                          TileCfg<BN>::kSmemBytes, stream, p);
   else
-    grouped_gemm_kernel<MODE, BN, false><<<num_sms, kGemmThreads, TileCfg<BN>::kSmemBytes, stream>>>(p);
-  return cudaGetLastError();
+    return launch_chained(grouped_gemm_kernel<MODE, BN, false>, dim3(num_sms), dim3(kGemmThreads),
+                          TileCfg<BN>::kSmemBytes, stream, p);
 }
 
 template <int MODE, int BN>

@@ -115,6 +115,10 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
+  // Everything above touched only this CTA's own state; global memory written by earlier
+  // kernels is read from here on.
+  chain_wait();
+  chain_release();
   const int m_tiles = p.meta[0];
   const int total_items = m_tiles * p.n_tiles;
   const int kblocks = p.kblocks;
@@ -309,8 +313,7 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
 
 template <int MODE, int NT>
 cudaError_t launch_one(const GemmParams& p, int num_sms, cudaStream_t stream) {
-  decode_gemm_kernel<MODE, NT><<<num_sms, kThreads, DCfg<NT>::kSmemBytes, stream>>>(p);
-  return cudaGetLastError();
+  return launch_chained(decode_gemm_kernel<MODE, NT>, dim3(num_sms), dim3(kThreads), DCfg<NT>::kSmemBytes, stream, p);
 }
 
 template <int MODE, int NT>

@@ -22,6 +22,8 @@ __global__ void __launch_bounds__(256)
 scan_kernel(Workspace ws, int e_local, int n_chunks, int pad_rows) {
   __shared__ int s_scan[256];
   const int e = threadIdx.x;
+  chain_wait();
+  chain_release();
   int* chunk_counts = ws.at<int>(ws.L.chunk_counts);
   int* chunk_base = ws.at<int>(ws.L.chunk_base);
   int total = 0;
@@ -73,6 +75,8 @@ __global__ void __launch_bounds__(256)
 place_kernel(Workspace ws, const int32_t* __restrict__ ids, long long ids_stride,
              const float* __restrict__ w, long long w_stride, int T, int local_off, int e_local) {
   __shared__ int s_ids[kTopK][kChunkTokens];   // [k][token]: conflict-free when lanes walk tokens
+  chain_wait();
+  chain_release();
   const int c = blockIdx.x;
   const int t0 = c * kChunkTokens;
   for (int i = threadIdx.x; i < kChunkTokens * kTopK; i += blockDim.x) {
@@ -122,6 +126,8 @@ gather_kernel(Workspace ws, const uint8_t* __restrict__ hidden, long long hidden
               const float* __restrict__ hscale, long long sstride_t, long long sstride_kb, int hidden_dim) {
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
+  chain_wait();
+  chain_release();
   const int rows = ws.at<int>(ws.L.meta)[1];
   const int* row_token = ws.at<int>(ws.L.row_token);
   uint8_t* a_packed = ws.at<uint8_t>(ws.L.a_packed);
@@ -149,20 +155,18 @@ cudaError_t launch_permute(const Workspace& ws, const int32_t* ids, long long id
                            const float* hscale, long long sstride_t, long long sstride_kb, int T, int e_local,
                            int local_off, int hidden_dim, int pad_rows, int num_sms, cudaStream_t stream) {
   const int n_chunks = (T + kChunkTokens - 1) / kChunkTokens;
-  scan_kernel<<<1, 256, 0, stream>>>(ws, e_local, n_chunks, pad_rows);
-  cudaError_t err = cudaGetLastError();
+  cudaError_t err = launch_chained(scan_kernel, dim3(1), dim3(256), 0, stream, ws, e_local, n_chunks, pad_rows);
   if (err != cudaSuccess) return err;
   if (n_chunks > 0) {
-    place_kernel<<<n_chunks, 256, 0, stream>>>(ws, ids, ids_stride, w, w_stride, T, local_off, e_local);
-    err = cudaGetLastError();
+    err = launch_chained(place_kernel, dim3(n_chunks), dim3(256), 0, stream, ws, ids, ids_stride, w, w_stride, T,
+                         local_off, e_local);
     if (err != cudaSuccess) return err;
     long long cap_rows = ws.L.m_cap;
     int blocks = (int)((cap_rows + 7) / 8);
     int cap = num_sms * 8;
     if (blocks > cap) blocks = cap;
-    gather_kernel<<<blocks, 256, 0, stream>>>(ws, hidden, hidden_row_stride, hscale, sstride_t, sstride_kb,
-                                              hidden_dim);
-    err = cudaGetLastError();
+    err = launch_chained(gather_kernel, dim3(blocks), dim3(256), 0, stream, ws, hidden, hidden_row_stride, hscale,
+                         sstride_t, sstride_kb, hidden_dim);
   }
   return err;
 }

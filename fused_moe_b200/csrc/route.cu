@@ -42,6 +42,7 @@ route_kernel(const void* __restrict__ logits, int logits_dtype, const void* __re
              int32_t* __restrict__ topk_ids, float* __restrict__ topk_w, int* __restrict__ chunk_counts) {
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
+  chain_release();   // launched in plain stream order itself; the kernel after it may become resident early
   // Lane L owns expert g*32+L of every group g, so a group reduction is a warp reduction.
   float b[kNumGroups];
 #pragma unroll
@@ -125,6 +126,7 @@ route_kernel(const void* __restrict__ logits, int logits_dtype, const void* __re
 __global__ void __launch_bounds__(256)
 count_kernel(const int32_t* __restrict__ ids, long long row_stride, int T, int local_off, int e_local,
              int* __restrict__ chunk_counts) {
+  chain_release();
   long long n = (long long)T * kTopK;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     int t = (int)(i / kTopK), k = (int)(i % kTopK);
