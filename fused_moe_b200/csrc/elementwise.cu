@@ -65,9 +65,9 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ tok_
   chain_wait();
   chain_release();
   const int vec_per_row = hidden / 8;   // 8 bf16 = 16 bytes
-  const long long n = (long long)T * vec_per_row;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
-    const int t = (int)(i / vec_per_row), v = (int)(i % vec_per_row);
+  // One block per token (block-stride): the token's eight row numbers are sorted once per
+  // thread and then reused for all of the thread's 16-byte column groups.
+  for (int t = blockIdx.x; t < T; t += gridDim.x) {
     int rows[kTopK];
     {
       const int4 a = reinterpret_cast<const int4*>(tok_rows + (size_t)t * kTopK)[0];
@@ -75,7 +75,7 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ tok_
       rows[0] = a.x; rows[1] = a.y; rows[2] = a.z; rows[3] = a.w;
       rows[4] = b.x; rows[5] = b.y; rows[6] = b.z; rows[7] = b.w;
     }
-    // ascending order with -1 (not local) last: 8-element insertion sort on keys
+    // ascending order with -1 (not local) last: 8-element insertion sort on unsigned keys
 #pragma unroll
     for (int a = 1; a < kTopK; ++a) {
 #pragma unroll
@@ -84,27 +84,37 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ tok_
         if (z < x) { rows[b - 1] = (int)z; rows[b] = (int)x; }
       }
     }
-    float acc[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-#pragma unroll
-    for (int k = 0; k < kTopK; ++k) {
-      if (rows[k] < 0) break;
-      const uint4 raw = reinterpret_cast<const uint4*>(y + (size_t)rows[k] * hidden)[v];
-      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __bfloat1622float2(p2[j]);
-        // bf16 + bf16 in fp32 is exact before the rounding, so this equals a bf16 addition
-        acc[2 * j] = __bfloat162float(__float2bfloat16_rn(acc[2 * j] + f.x));
-        acc[2 * j + 1] = __bfloat162float(__float2bfloat16_rn(acc[2 * j + 1] + f.y));
-      }
+    uint4* dst = reinterpret_cast<uint4*>(out + (size_t)t * stride);
+    if (rows[0] < 0) {   // no local expert took this token
+      for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) dst[v] = make_uint4(0u, 0u, 0u, 0u);
+      continue;
     }
-    uint4 pk;
-    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+    for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
+      uint4 raw[kTopK];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-    *reinterpret_cast<uint4*>(out + (size_t)t * stride + 8 * v) = pk;
+      for (int k = 0; k < kTopK; ++k)
+        if (rows[k] >= 0) raw[k] = reinterpret_cast<const uint4*>(y + (size_t)rows[k] * hidden)[v];
+      float acc[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+      for (int k = 0; k < kTopK; ++k) {
+        if (rows[k] < 0) break;
+        const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw[k]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __bfloat1622float2(p2[j]);
+          // bf16 + bf16 in fp32 is exact before the rounding, so this equals a bf16 addition
+          acc[2 * j] = __bfloat162float(__float2bfloat16_rn(acc[2 * j] + f.x));
+          acc[2 * j + 1] = __bfloat162float(__float2bfloat16_rn(acc[2 * j + 1] + f.y));
+        }
+      }
+      uint4 pk;
+      __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+      dst[v] = pk;
+    }
   }
 }
 
@@ -142,9 +152,8 @@ cudaError_t launch_requant(const Workspace& ws, int inter, int num_sms, cudaStre
 cudaError_t launch_combine(const Workspace& ws, int T, int hidden, void* out_bf16, long long out_row_stride,
                            int num_sms, cudaStream_t stream) {
   if (T <= 0) return cudaSuccess;
-  long long n = (long long)T * (hidden / 8);
-  int blocks = (int)((n + 255) / 256);
-  int cap = num_sms * 16;
+  int blocks = T;
+  const int cap = num_sms * 8;   // 8 blocks of 256 threads are resident per SM
   if (blocks > cap) blocks = cap;
   return launch_chained(combine_kernel, dim3(blocks), dim3(256), 0, stream,
                         (const __nv_bfloat16*)ws.at<__nv_bfloat16>(ws.L.y), (const int*)ws.at<int>(ws.L.tok_rows), T,

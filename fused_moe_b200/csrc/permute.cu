@@ -28,9 +28,16 @@ scan_kernel(Workspace ws, int e_local, int n_chunks, int pad_rows) {
   int* chunk_base = ws.at<int>(ws.L.chunk_base);
   int total = 0;
   if (e < e_local) {
-    for (int c = 0; c < n_chunks; ++c) {
-      chunk_base[c * e_local + e] = total;
-      total += chunk_counts[c * e_local + e];
+    // eight independent loads in flight per round instead of one load per chunk in a chain
+    for (int c0 = 0; c0 < n_chunks; c0 += 8) {
+      int cnt[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) cnt[j] = c0 + j < n_chunks ? chunk_counts[(c0 + j) * e_local + e] : 0;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (c0 + j < n_chunks) chunk_base[(c0 + j) * e_local + e] = total;
+        total += cnt[j];
+      }
     }
   }
   int padded = (total + pad_rows - 1) / pad_rows * pad_rows;   // 128, or 256 when CTA pairs run the GEMMs
