@@ -495,12 +495,15 @@ def run_profile_case(args):
         raw = ws.view("meta", torch.int64, (32,)).cpu().numpy()      # meta + its padding, as u64 words
         names = ("wait_acc", "promote", "mma_issue", "kblocks", "epi_role_total", "tile_epilogues", "unused2",
                  "mma_wait_epilogue", "mma_wait_tma")
+        if args.tokens <= 16 and os.environ.get("B200MOE_DECODE", "") != "0":   # the decode kernels' counters
+            names = ("prod_wait_stage", "prod_issue", "prod_total", "kblocks", "mma_wait_acc", "mma_wait_tma",
+                     "mma_issue", "promo_wait_acc", "promo_total")
         prof = {"gemm1": dict(zip(names, (int(x) for x in raw[4:13]))),
                 "gemm2": dict(zip(names, (int(x) for x in raw[17:26])))}
         # eight cycle stamps per K block of CTA 0: issuer wait start, operands landed, accumulator free,
         # MMAs issued; promotion warp 0: accumulator ready, first chunks read, accumulator released, done
         tr = ws.view("trace", torch.int64, (2, 64, 8)).cpu().numpy()
-        for name, t in (("gemm1", tr[0]), ("gemm2", tr[1])):
+        for name, t in (("gemm1", tr[0]), ("gemm2", tr[1])) if args.tokens > 16 else ():
             base = int(t[8, 0])
             prof[name]["trace_kb8_31"] = [[int(x) - base for x in t[i]] for i in range(8, 32)]
     print(json.dumps({"profile_case": "slice32", "tokens": args.tokens, "zipf": args.zipf, "status": code,

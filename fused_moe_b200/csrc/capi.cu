@@ -101,6 +101,27 @@ int make_tmap(CUtensorMap* map, const void* base, uint64_t rows, uint64_t k, uin
   return B200MOE_OK;
 }
 
+// GEMM1 weights [e_local][2*inter][k] seen as planes: plane 2e holds expert e's gate rows, plane
+// 2e+1 its up rows.  One box = the same `box_rows` rows of two consecutive planes (gate rows,
+// then the matching up rows), 128 bytes of K wide, 128-byte swizzle: one TMA operation
+// instead of two per K block (a box costs the issuing thread and the TMA unit a few hundred
+// cycles whatever its size).
+int make_tmap_gate_up(CUtensorMap* map, const void* base, uint64_t e_local, uint64_t inter, uint64_t k,
+                      uint32_t box_rows) {
+  cuuint64_t dims[3] = {k, inter, 2 * e_local};
+  cuuint64_t strides[2] = {k, inter * k};
+  cuuint32_t box[3] = {(cuuint32_t)kBlockK, box_rows, 2};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    snprintf(g_cuda_error, sizeof(g_cuda_error), "cuTensorMapEncodeTiled (3D) failed with CUresult %d", (int)r);
+    return B200MOE_ERR_CUDA;
+  }
+  return B200MOE_OK;
+}
+
 // (token, k) pairs up to which the 128-wide N tile is used.  Measured on the 32-expert slice at 32..1024
 // tokens the 256-wide tile is as fast or faster everywhere but at 128 tokens (-6 %), so the narrow tile
 // is only reachable through B200MOE_BN=128.
@@ -130,6 +151,7 @@ void compute_layout(int T, int e_local, int hidden, int inter, b200moe_ws_layout
   auto take = [&](uint64_t bytes) { uint64_t o = off; off = align_up(off + bytes, 256); return o; };
   L->status = take(16 * 4);
   L->meta = take(8 * 4);
+  L->splitk_count = take(2 * kSplitKSlots * 4);   // inside the range that clear_counters() zeroes
   L->chunk_counts = take((uint64_t)n_chunks * e_local * 4);
   L->chunk_base = take((uint64_t)n_chunks * e_local * 4);
   L->expert_count = take((uint64_t)e_local * 4);
@@ -148,6 +170,7 @@ void compute_layout(int T, int e_local, int hidden, int inter, b200moe_ws_layout
   L->topk_ids = take((uint64_t)(T > 0 ? T : 1) * kTopK * 4);
   L->topk_w = take((uint64_t)(T > 0 ? T : 1) * kTopK * 4);
   L->trace = take(2 * 8 * 64 * 8);   // B200MOE_PROF: absolute cycle stamps of CTA 0's first 64 K blocks
+  L->splitk_scratch = take((uint64_t)kSplitKSlots * kSplitKMax * 16 * 128 * 4);   // 2 MiB
   L->total_bytes = off;
 }
 
@@ -164,7 +187,7 @@ int bind_workspace(int T, int e_local, int hidden, int inter, void* workspace, s
 
 // Clears the status word and the histogram (start of a layer call).
 int clear_counters(const Workspace& ws, int e_local, cudaStream_t stream) {
-  // status, meta, chunk_counts are adjacent: one memset covers them
+  // status, meta, splitk_count, chunk_counts are adjacent: one memset covers them
   size_t bytes = (size_t)(ws.L.chunk_counts - ws.L.status) + (size_t)ws.L.n_chunks * e_local * 4;
   CUDA_TRY(cudaMemsetAsync(ws.base + ws.L.status, 0, bytes, stream));
   return B200MOE_OK;
@@ -304,9 +327,11 @@ int b200moe_experts(const int32_t* topk_ids, int64_t ids_row_stride, const float
                       nt ? nt : kTileM)) != B200MOE_OK)
     return rc;
   if (use_pairs && (hidden % 256 != 0 || inter % 128 != 0)) return B200MOE_ERR_UNSUPPORTED_SHAPE;
-  if ((rc = make_tmap(&g1.tmap_b, w1, (uint64_t)e_local * 2 * inter, (uint64_t)hidden, (uint64_t)hidden, bn / 2)) !=
-      B200MOE_OK)
-    return rc;
+  if (!use_pairs)   // one box = bn/2 gate rows + the matching bn/2 up rows (decode kernels: 64 + 64)
+    rc = make_tmap_gate_up(&g1.tmap_b, w1, (uint64_t)e_local, (uint64_t)inter, (uint64_t)hidden, bn / 2);
+  else
+    rc = make_tmap(&g1.tmap_b, w1, (uint64_t)e_local * 2 * inter, (uint64_t)hidden, (uint64_t)hidden, bn / 2);
+  if (rc != B200MOE_OK) return rc;
   g1.meta = ws.at<int>(ws.L.meta);
   g1.tile_expert = ws.at<int>(ws.L.tile_expert);
   g1.row_token = ws.at<int>(ws.L.row_token);
@@ -322,6 +347,8 @@ int b200moe_experts(const int32_t* topk_ids, int64_t ids_row_stride, const float
   g1.act = ws.at<__half>(ws.L.act);
   g1.row_amax = ws.at<unsigned>(ws.L.row_amax);
   g1.status = ws.at<int>(ws.L.status);
+  g1.splitk_scratch = ws.at<float>(ws.L.splitk_scratch);
+  g1.splitk_count = ws.at<int>(ws.L.splitk_count);
   // B200MOE_PROF=1: CTA 0 adds cycle counters into the padding after `meta`
   // (GEMM1: 9 x u64 at meta+32, GEMM2: at meta+136); cleared with the counters each call.
   static const bool prof_on = getenv("B200MOE_PROF") != nullptr;
@@ -341,8 +368,8 @@ int b200moe_experts(const int32_t* topk_ids, int64_t ids_row_stride, const float
   if ((rc = make_tmap(&g2.tmap_a, ws.base + ws.L.act_q, (uint64_t)ws.L.m_cap, (uint64_t)inter, (uint64_t)inter,
                       nt ? nt : kTileM)) != B200MOE_OK)
     return rc;
-  if ((rc = make_tmap(&g2.tmap_b, w2, (uint64_t)e_local * hidden, (uint64_t)inter, (uint64_t)inter, bn / 2)) !=
-      B200MOE_OK)
+  if ((rc = make_tmap(&g2.tmap_b, w2, (uint64_t)e_local * hidden, (uint64_t)inter, (uint64_t)inter,
+                      !use_pairs ? bn : bn / 2)) != B200MOE_OK)   // the whole B tile (decode: the 128-row slab) in one box
     return rc;
   g2.meta = g1.meta;
   g2.tile_expert = g1.tile_expert;
@@ -359,6 +386,8 @@ int b200moe_experts(const int32_t* topk_ids, int64_t ids_row_stride, const float
   g2.row_weight = ws.at<float>(ws.L.row_weight);
   g2.y = ws.at<__nv_bfloat16>(ws.L.y);
   g2.status = g1.status;
+  g2.splitk_scratch = g1.splitk_scratch;
+  g2.splitk_count = g1.splitk_count + kSplitKSlots;
   g2.prof = prof_on ? ws.at<unsigned long long>(ws.L.meta + 136) : nullptr;
   g2.trace = prof_on ? ws.at<unsigned long long>(ws.L.trace) + 8 * 64 : nullptr;
   if (nt) CUDA_TRY(launch_decode_gemm(2, nt, g2, num_sms, st));

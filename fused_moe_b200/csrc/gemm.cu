@@ -7,7 +7,7 @@
 //
 // One CTA per SM walks work items (M tile of 128 packed rows, N tile of BN weight rows).
 // Per 128-wide K block (= one fp32 scale block, = one 128-byte swizzled TMA row):
-//   warps 0, 3  TMA producers (one lane each, alternate K blocks): A box 128x128 B and two B boxes (BN/2)x128 B into a smem ring
+//   warps 0, 3  TMA producers (one lane each, alternate K blocks): A box 128x128 B and one B box BNx128 B into a smem ring
 //   warps 1, 2  (one lane each, alternate K blocks) issue 4 tcgen05.mma (K=32 each) into one of two TMEM accumulators, starting
 //               from zero, so each accumulator holds the raw e4m3 dot product of one K block
 //   warps 4-11  read that accumulator back (tcgen05.ld, two loads in flight) and fold it into
@@ -137,14 +137,8 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x) {
         const int m_tile = w / p.n_tiles, n_tile = w % p.n_tiles;
         const int e = p.tile_expert[m_tile];
-        int brow0, brow1;
-        if (MODE == 1) {
-          brow0 = e * p.n_per_expert + n_tile * (BN / 2);
-          brow1 = brow0 + p.inter;
-        } else {
-          brow0 = e * p.n_per_expert + n_tile * BN;
-          brow1 = brow0 + BN / 2;
-        }
+        // GEMM1: first row inside the gate (and up) plane of expert e; GEMM2: row of [e_local*hidden][inter]
+        const int brow = MODE == 1 ? n_tile * (BN / 2) : e * p.n_per_expert + n_tile * BN;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           if ((it & 1u) != pme) continue;
           const uint32_t s = it % S, ph = (it / S) & 1u;
@@ -153,8 +147,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           const uint32_t a_dst = smem_base + s * Cfg::kStageBytes;
           mbar_arrive_expect_tx(full, Cfg::kStageBytes);
           tma_load_2d(a_dst, &p.tmap_a, kb * kBlockK, m_tile * kTileM, full);
-          tma_load_2d(a_dst + kABytes, &p.tmap_b, kb * kBlockK, brow0, full);
-          tma_load_2d(a_dst + kABytes + (BN / 2) * kBlockK, &p.tmap_b, kb * kBlockK, brow1, full);
+          // the whole B tile in one operation: BN/2 gate rows + BN/2 up rows (3D box over the two planes), or BN rows
+          if (MODE == 1) tma_load_3d(a_dst + kABytes, &p.tmap_b, kb * kBlockK, brow, 2 * e, full);
+          else tma_load_2d(a_dst + kABytes, &p.tmap_b, kb * kBlockK, brow, full);
         }
       }
       // Copies still in flight must land before the CTA's shared memory is released.

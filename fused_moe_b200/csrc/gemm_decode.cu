@@ -11,6 +11,13 @@
 // whose own small-batch configuration also swaps A and B, moe_gemm.cu:614-648): raw e4m3 dot
 // product per K block, promoted in fp32 registers with the fp32 block scales.
 //
+// Weights arrive as ONE TMA box per K block (GEMM1: a 3D box over the expert's gate and up
+// planes), issued by four producer threads in turn: a box costs its issuing thread a few hundred
+// cycles whatever its size.  When a call has fewer (expert tile, slab) items than half the SMs,
+// the K range of an item is split over 2 or 4 CTAs (one SM draws ~50 GB/s from HBM at most):
+// every piece leaves fp32 partial sums in scratch and the CTA that arrives last adds them in
+// piece order and runs the epilogue, so results stay run-to-run identical.
+//
 // Work item = (expert tile, slab of 128 weight rows).  GEMM1's slab is 64 gate rows plus the
 // 64 matching up rows, so lanes 0-63 hold g and lanes 64-127 hold u of the same columns; the
 // up warps hand u over through shared memory and the gate warps write g*silu(u) (fp16) and
@@ -26,7 +33,8 @@ namespace b200moe {
 
 namespace {
 
-constexpr int kThreads = 256;            // warps 0-3 control (0 and 3: TMA, 1 and 2: MMA), warps 4-7 promotion
+constexpr int kThreads = 320;            // warps 0-3 control (0 and 3: TMA, 1 and 2: MMA), warps 4-7 promotion, warps 8-9: TMA
+constexpr int kProducers = 4;            // a TMA box costs its issuing thread a few hundred cycles: four threads take turns
 constexpr int kSlabRows = 128;
 constexpr int kWBytes = kSlabRows * kBlockK;   // 16 KiB of weights per stage
 constexpr int kRing = 4;                 // accumulators in tensor memory
@@ -61,7 +69,7 @@ __device__ __forceinline__ void tmem_ld_wait_on16(uint32_t (&a)[16]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" : B200MOE_RW8(a, 0), B200MOE_RW8(a, 8) : : "memory");
 }
 
-template <int MODE, int NT>
+template <int MODE, int NT, bool PROF>
 __global__ void __launch_bounds__(kThreads, 1)
 decode_gemm_kernel(const __grid_constant__ GemmParams p) {
   using Cfg = DCfg<NT>;
@@ -79,8 +87,10 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
   const uint32_t bar_drain = bar_tempty + 8 * kRing;
   const uint32_t bar_xready = bar_drain + 16;    // 2 barriers: u of an up warp is in shared memory
   const uint32_t bar_xfree = bar_xready + 16;    // 2 barriers: its gate warp has read it
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 2 * kRing + 6);
+  const uint32_t bar_split = bar_xfree + 16;     // 2 barriers (split K): partial sums written; arrival order known
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 2 * kRing + 8);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* split_flag = reinterpret_cast<volatile int*>(tmem_slot + 3);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -100,6 +110,8 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
       mbar_init(bar_xready + 8 * i, 1);
       mbar_init(bar_xfree + 8 * i, 1);
     }
+    mbar_init(bar_split, 4);
+    mbar_init(bar_split + 8, 1);
     abort_flag[0] = 0;
     abort_flag[1] = 0;
     fence_mbar_init();
@@ -120,41 +132,60 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
   chain_wait();
   chain_release();
   const int m_tiles = p.meta[0];
-  const int total_items = m_tiles * p.n_tiles;
+  const int tiles = m_tiles * p.n_tiles;
   const int kblocks = p.kblocks;
+  // Split K: with few active experts fewer (expert tile, slab) items exist than SMs, and one SM
+  // pulls at most ~50 GB/s from HBM, so the K range of an item is cut into KS pieces on KS CTAs.
+  // Each piece leaves its fp32 partial sums in scratch; the CTA that arrives last on the item's
+  // counter adds the pieces in piece order (deterministic) and runs the epilogue.
+  int KS = 1;
+  if (NT == 16 && p.splitk_scratch != nullptr && tiles > 0 && tiles <= kSplitKSlots) {
+    const int want = (int)gridDim.x / tiles;
+    if (want >= 4 && kblocks % 4 == 0 && kblocks / 4 >= 8) KS = 4;
+    else if (want >= 2 && kblocks % 2 == 0 && kblocks / 2 >= 8) KS = 2;
+  }
+  const int kbs = kblocks / KS;          // K blocks per piece
+  const int total_items = tiles * KS;    // item w = (tile w / KS, piece w % KS)
 
-  if (warp == 0 || warp == 3) {
+  if (warp == 0 || warp == 3 || warp >= 8) {
     if (lane == 0) {
-      // ------------------------------ TMA producers (alternate K blocks) ------------------------------
-      const uint32_t pme = warp == 0 ? 0u : 1u;
+      // ------------------------------ TMA producers (every fourth K block each) ------------------------------
+      const uint32_t pme = warp == 0 ? 0u : (warp == 3 ? 1u : (uint32_t)(warp - 6));
       uint32_t it = 0;
       bool alive = true;
+      long long pw = 0, pi = 0;
+      const long long pbegin = PROF ? clock64() : 0;
       for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x) {
-        const int m_tile = w / p.n_tiles, slab = w % p.n_tiles;
+        const int tile = w / KS, ks = w % KS;
+        const int m_tile = tile / p.n_tiles, slab = tile % p.n_tiles;
         const int e = p.tile_expert[m_tile];
-        int wrow0, wrow1;
-        if (MODE == 1) {
-          wrow0 = e * p.n_per_expert + slab * 64;        // 64 gate rows
-          wrow1 = wrow0 + p.inter;                       // the matching 64 up rows
-        } else {
-          wrow0 = e * p.n_per_expert + slab * kSlabRows;
-          wrow1 = wrow0 + 64;
-        }
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          if ((it & 1u) != pme) continue;
+        // GEMM1: 64 gate rows + the matching 64 up rows of expert e, one 3D box over its two planes;
+        // GEMM2: 128 consecutive rows of [e_local*hidden][inter]
+        const int wrow = MODE == 1 ? slab * 64 : e * p.n_per_expert + slab * kSlabRows;
+        for (int kb = ks * kbs; kb < (ks + 1) * kbs; ++kb, ++it) {
+          if ((it % kProducers) != pme) continue;
           const uint32_t s = it % S, ph = (it / S) & 1u;
+          const long long q0 = PROF ? clock64() : 0;
           if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status, 21)) { alive = false; break; }
+          const long long q1 = PROF ? clock64() : 0;
           const uint32_t full = bar_full + 8 * s;
           const uint32_t w_dst = smem_base + s * Cfg::kStageBytes;
           mbar_arrive_expect_tx(full, Cfg::kStageBytes);
-          tma_load_2d(w_dst, &p.tmap_b, kb * kBlockK, wrow0, full);
-          tma_load_2d(w_dst + 64 * kBlockK, &p.tmap_b, kb * kBlockK, wrow1, full);
+          if (MODE == 1) tma_load_3d(w_dst, &p.tmap_b, kb * kBlockK, wrow, 2 * e, full);
+          else tma_load_2d(w_dst, &p.tmap_b, kb * kBlockK, wrow, full);
           tma_load_2d(w_dst + kWBytes, &p.tmap_a, kb * kBlockK, m_tile * kTileM, full);
+          if (PROF) { pw += q1 - q0; pi += clock64() - q1; }
         }
+      }
+      if (PROF && p.prof && blockIdx.x == 0 && pme == 0) {
+        p.prof[0] = (unsigned long long)pw;                     // producer 0: waiting for a free stage
+        p.prof[1] = (unsigned long long)pi;                     // producer 0: expect_tx + two TMA issues
+        p.prof[2] = (unsigned long long)(clock64() - pbegin);   // producer 0: whole loop
+        p.prof[3] = (unsigned long long)it;                     // K blocks of CTA 0
       }
       const uint32_t first = it > (uint32_t)S ? it - S : 0u;
       for (uint32_t j = first; j < it; ++j)
-        if ((j & 1u) == pme) (void)mbar_wait(bar_full + 8 * (j % S), (j / S) & 1u, abort_flag + 1, p.status, 26);
+        if ((j % kProducers) == pme) (void)mbar_wait(bar_full + 8 * (j % S), (j / S) & 1u, abort_flag + 1, p.status, 26);
     }
   } else if (warp == 1 || warp == 2) {
     if (lane == 0) {
@@ -163,32 +194,45 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
       const uint32_t me = (uint32_t)(warp - 1);
       uint32_t it = 0;
       bool alive = true;
+      long long iw0 = 0, iw1 = 0, ii = 0;
       for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x) {
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
+        for (int kb = 0; kb < kbs; ++kb, ++it) {
           if ((it & 1u) != me) continue;
           const uint32_t s = it % S, ph = (it / S) & 1u;
           const uint32_t b = it % kRing, bph = (it / kRing) & 1u;
+          const long long q0 = PROF ? clock64() : 0;
           if (!mbar_wait(bar_tempty + 8 * b, bph ^ 1u, abort_flag, p.status, 22)) { alive = false; break; }
+          const long long q1 = PROF ? clock64() : 0;
           if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 23)) { alive = false; break; }
+          const long long q2 = PROF ? clock64() : 0;
           tc_fence_after();
           const uint32_t w_addr = smem_base + s * Cfg::kStageBytes;
           tc_mma_f8_kblock(tmem_base + b * NT, kmajor_sw128_desc_lo(w_addr), kmajor_sw128_desc_lo(w_addr + kWBytes),
                            kKmajorSw128DescHi, idesc);
           tc_commit(bar_empty + 8 * s);
           tc_commit(bar_tfull + 8 * b);
+          if (PROF) { iw0 += q1 - q0; iw1 += q2 - q1; ii += clock64() - q2; }
         }
       }
       tc_commit(bar_drain + 8 * me);
       (void)mbar_wait(bar_drain + 8 * me, 0u, abort_flag + 1, p.status, 25);
+      if (PROF && p.prof && blockIdx.x == 0 && me == 0) {
+        p.prof[4] = (unsigned long long)iw0;   // issuer 0: waiting for a free accumulator
+        p.prof[5] = (unsigned long long)iw1;   // issuer 0: waiting for operands
+        p.prof[6] = (unsigned long long)ii;    // issuer 0: MMAs + commits
+      }
     }
-  } else if (warp >= 4) {
+  } else if (warp >= 4 && warp < 8) {
     // ------------------------------ promotion + epilogue ------------------------------
     const int q = warp & 3;                 // TMEM lane quarter: weight rows 32q .. 32q+31 of the slab
-    uint32_t it = 0, xi = 0;
+    uint32_t it = 0, xi = 0, si = 0;
     bool alive = true;
+    long long ew_wait = 0;
+    const long long ebegin = PROF ? clock64() : 0;
     const int nblk_per_expert = p.n_per_expert / kBlockK;
     for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x) {
-      const int m_tile = w / p.n_tiles, slab = w % p.n_tiles;
+      const int tile = w / KS, ks = w % KS;
+      const int m_tile = tile / p.n_tiles, slab = tile % p.n_tiles;
       const int e = p.tile_expert[m_tile];
       const int row0 = m_tile * kTileM;     // the expert's first packed row; its rows are row0 .. row0+cnt-1
       float acc[NT];
@@ -216,7 +260,7 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
       }
       __syncwarp();
 
-      for (int kb = 0; kb < kblocks; ++kb, ++it) {
+      for (int kb = ks * kbs; kb < (ks + 1) * kbs; ++kb, ++it) {
         const uint32_t b = it % kRing, bph = (it / kRing) & 1u;
         float4 sa_c[NT / 4];
         if (MODE == 1) {
@@ -224,10 +268,12 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
           for (int j = 0; j < NT / 4; ++j) sa_c[j] = reinterpret_cast<const float4*>(panel + kb * NT)[j];
         }
         const float sb_cur = panel_sb[kb];
+        const long long e0 = PROF ? clock64() : 0;
         bool ok = mbar_wait(bar_tfull + 8 * b, bph, abort_flag, p.status, 24);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) { alive = false; break; }
         tc_fence_after();
+        if (PROF) ew_wait += clock64() - e0;
         const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + b * NT;
         if constexpr (NT == 16) {
           uint32_t r[16];
@@ -259,6 +305,40 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
         }
       }
       if (!alive) break;
+
+      if (KS > 1) {
+        float* scr_tile = p.splitk_scratch + (size_t)tile * KS * NT * kSlabRows;
+        float* scr = scr_tile + (size_t)ks * NT * kSlabRows + q * 32 + lane;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) scr[j * kSlabRows] = acc[j];
+        __threadfence();
+        __syncwarp();
+        const uint32_t sph = si & 1u;
+        ++si;
+        if (lane == 0) mbar_arrive(bar_split);          // all four promotion warps have published their pieces
+        bool oks = mbar_wait(bar_split, sph, abort_flag, p.status, 29);
+        oks = __all_sync(0xffffffffu, oks);
+        if (!oks) { alive = false; break; }
+        if (warp == 4 && lane == 0) {
+          __threadfence();   // the other warps' pieces (ordered before this point by the barrier) before the count
+          const int prev = atomicAdd(p.splitk_count + tile, 1);
+          if (prev == KS - 1) p.splitk_count[tile] = 0;   // every piece has arrived: leave the counter clean
+          *split_flag = prev;
+          mbar_arrive(bar_split + 8);
+        }
+        oks = mbar_wait(bar_split + 8, sph, abort_flag, p.status, 30);
+        oks = __all_sync(0xffffffffu, oks);
+        if (!oks) { alive = false; break; }
+        if (*split_flag != KS - 1) continue;              // another CTA finishes this item
+        __threadfence();
+#pragma unroll
+        for (int j = 0; j < NT; ++j) acc[j] = 0.f;
+        for (int k = 0; k < KS; ++k) {
+          const float* src = scr_tile + (size_t)k * NT * kSlabRows + q * 32 + lane;
+#pragma unroll
+          for (int j = 0; j < NT; ++j) acc[j] += __ldcg(src + j * kSlabRows);
+        }
+      }
 
       const int cnt = min(p.expert_count[e], NT);   // real rows of this expert
       if (MODE == 1) {
@@ -304,6 +384,10 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
         }
       }
     }
+    if (PROF && p.prof && blockIdx.x == 0 && warp == 4 && lane == 0) {
+      p.prof[7] = (unsigned long long)ew_wait;                  // promotion warp 0: waiting for an accumulator
+      p.prof[8] = (unsigned long long)(clock64() - ebegin);     // promotion warp 0: whole role
+    }
   }
 
   tc_fence_before();
@@ -313,12 +397,19 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
 
 template <int MODE, int NT>
 cudaError_t launch_one(const GemmParams& p, int num_sms, cudaStream_t stream) {
-  return launch_chained(decode_gemm_kernel<MODE, NT>, dim3(num_sms), dim3(kThreads), DCfg<NT>::kSmemBytes, stream, p);
+  if (p.prof)
+    return launch_chained(decode_gemm_kernel<MODE, NT, true>, dim3(num_sms), dim3(kThreads), DCfg<NT>::kSmemBytes,
+                          stream, p);
+  return launch_chained(decode_gemm_kernel<MODE, NT, false>, dim3(num_sms), dim3(kThreads), DCfg<NT>::kSmemBytes,
+                        stream, p);
 }
 
 template <int MODE, int NT>
 cudaError_t configure_one() {
-  return cudaFuncSetAttribute(decode_gemm_kernel<MODE, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(decode_gemm_kernel<MODE, NT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       DCfg<NT>::kSmemBytes);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(decode_gemm_kernel<MODE, NT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               DCfg<NT>::kSmemBytes);
 }
 

@@ -19,6 +19,11 @@ cudaError_t launch_permute(const Workspace& ws, const int32_t* ids, long long id
                            const float* hscale, long long sstride_t, long long sstride_kb, int T, int e_local,
                            int local_off, int hidden_dim, int pad_rows, int num_sms, cudaStream_t stream);
 
+// Decode GEMMs split the K range of a weight slab over up to kSplitKMax CTAs when a call has at
+// most kSplitKSlots (expert tile, slab) items, i.e. fewer than half of the SMs would stream weights.
+constexpr int kSplitKSlots = 64;
+constexpr int kSplitKMax = 4;
+
 // Arguments of the two grouped GEMMs.  `tmap_a` covers the packed rows [m_cap][K],
 // `tmap_b` the weights viewed as [e_local * N][K]; both e4m3, 128-byte swizzled boxes.
 struct GemmParams {
@@ -42,6 +47,8 @@ struct GemmParams {
   const float* row_weight;  // GEMM2 in: routing weight per row
   __nv_bfloat16* y;         // GEMM2 out: [m_cap][hidden] bf16 rows, already scaled by weight
   int* status;
+  float* splitk_scratch;    // decode GEMMs: [kSplitKSlots][kSplitKMax][16][128] partial sums
+  int* splitk_count;        // decode GEMMs: arrivals per weight slab, zero at kernel start and end
   unsigned long long* prof;   // optional cycle counters of CTA 0 (null: off)
   unsigned long long* trace;  // optional [64][4] absolute cycle stamps of CTA 0's first K blocks
 };

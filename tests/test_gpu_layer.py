@@ -73,18 +73,18 @@ def test_benchmark_shape_against_oracle(T, tseed, zipf, full_weights_cpu, full_w
     assert frac_all >= 0.999 and frac_nz >= 0.999, (T, frac_all, frac_nz, max_abs)
 
 
-def test_run_twice_is_bit_identical_up_to_reduction_order_and_out_argument():
+def test_run_twice_is_bit_identical_and_out_argument():
     g, inp = golden_inputs("layer_small_T200_off64")
     dev = torch.device("cuda", 0)
     gi = inp.to(dev)
     a = K.run(*gi.args()).clone()
     b = K.run(*gi.args()).clone()
-    # fp32 reductions into the output may land in a different order; everything before them is deterministic
-    assert (a.float() - b.float()).abs().max().item() <= 2 ** -6
+    # stable placement, fixed K order and a per-token combine in ascending expert order: no run-to-run variation
+    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
     own = torch.empty_like(a)
     r = K.custom_kernel(*gi.args(), out=own)
     assert r.data_ptr() == own.data_ptr()
-    assert (own.float() - a.float()).abs().max().item() <= 2 ** -6
+    assert torch.equal(own.view(torch.int16), a.view(torch.int16))
 
 
 def test_scale_layouts_and_bf16_logits():
