@@ -231,7 +231,12 @@ int b200moe_profile_next_gemm1(void* start_event, void* stop_event) {
 
 int b200moe_launches_per_run(int T, int e_local) {
   (void)e_local;
-  return T > 0 ? 8 : 0;   // route, scan, place, gather, gemm1, requant, gemm2, combine
+  if (T <= 0) return 0;
+  const char* front = getenv("B200MOE_FRONT");
+  const char* gemm = getenv("B200MOE_GEMM");
+  const bool fused_front = T <= kFrontSmallMaxTokens && !(front && front[0] == '0') && !(gemm && gemm[0] == 'p');
+  // route, scan, place, gather, gemm1, requant, gemm2, combine; decode-size calls fuse the first three
+  return fused_front ? 6 : 8;
 }
 
 int b200moe_route(const void* logits, int logits_dtype, const void* bias, int bias_dtype, int T,
@@ -270,12 +275,13 @@ int b200moe_count(const int32_t* topk_ids, int64_t ids_row_stride, int T, int lo
   return B200MOE_OK;
 }
 
-int b200moe_experts(const int32_t* topk_ids, int64_t ids_row_stride, const float* topk_w, int64_t w_row_stride,
-                    const uint8_t* hidden_states, int64_t hidden_row_stride, const float* hidden_scale,
-                    int64_t scale_stride_t, int64_t scale_stride_kb, const uint8_t* w1, const float* w1_scale,
-                    const uint8_t* w2, const float* w2_scale, int T, int e_local, int local_expert_offset,
-                    int hidden, int inter, void* workspace, size_t workspace_bytes, void* out_bf16,
-                    int64_t out_row_stride, void* stream) {
+// `placed`: routing, scan and placement of this call already ran as one kernel (front_small.cu).
+static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const float* topk_w, int64_t w_row_stride,
+                        const uint8_t* hidden_states, int64_t hidden_row_stride, const float* hidden_scale,
+                        int64_t scale_stride_t, int64_t scale_stride_kb, const uint8_t* w1, const float* w1_scale,
+                        const uint8_t* w2, const float* w2_scale, int T, int e_local, int local_expert_offset,
+                        int hidden, int inter, void* workspace, size_t workspace_bytes, void* out_bf16,
+                        int64_t out_row_stride, void* stream, bool placed) {
   if (!topk_ids || !topk_w || !w1 || !w1_scale || !w2 || !w2_scale) return B200MOE_ERR_INVALID_ARGUMENT;
   if (T > 0 && (!hidden_states || !hidden_scale || !out_bf16)) return B200MOE_ERR_INVALID_ARGUMENT;
   if (ids_row_stride < kTopK || w_row_stride < kTopK) return B200MOE_ERR_INVALID_ARGUMENT;
@@ -300,7 +306,7 @@ int b200moe_experts(const int32_t* topk_ids, int64_t ids_row_stride, const float
   }();
   CUDA_TRY(launch_permute(ws, topk_ids, ids_row_stride, topk_w, w_row_stride, hidden_states, hidden_row_stride,
                           hidden_scale, scale_stride_t, scale_stride_kb, T, e_local, local_expert_offset, hidden,
-                          use_pairs ? 2 * kTileM : kTileM, num_sms, st));
+                          use_pairs ? 2 * kTileM : kTileM, num_sms, st, placed));
 
   // small problems get the narrower N tile: more work items to spread over the SMs
   // Up to 16 tokens: swapped-operand decode kernels (B200MOE_DECODE=0 turns them off; B200MOE_DECODE=64
@@ -398,6 +404,17 @@ int b200moe_experts(const int32_t* topk_ids, int64_t ids_row_stride, const float
   return B200MOE_OK;
 }
 
+int b200moe_experts(const int32_t* topk_ids, int64_t ids_row_stride, const float* topk_w, int64_t w_row_stride,
+                    const uint8_t* hidden_states, int64_t hidden_row_stride, const float* hidden_scale,
+                    int64_t scale_stride_t, int64_t scale_stride_kb, const uint8_t* w1, const float* w1_scale,
+                    const uint8_t* w2, const float* w2_scale, int T, int e_local, int local_expert_offset,
+                    int hidden, int inter, void* workspace, size_t workspace_bytes, void* out_bf16,
+                    int64_t out_row_stride, void* stream) {
+  return experts_impl(topk_ids, ids_row_stride, topk_w, w_row_stride, hidden_states, hidden_row_stride, hidden_scale,
+                      scale_stride_t, scale_stride_kb, w1, w1_scale, w2, w2_scale, T, e_local, local_expert_offset,
+                      hidden, inter, workspace, workspace_bytes, out_bf16, out_row_stride, stream, false);
+}
+
 int b200moe_run(const void* logits, int logits_dtype, const void* bias, int bias_dtype, const uint8_t* hidden_states,
                 int64_t hidden_row_stride, const float* hidden_scale, int64_t scale_stride_t,
                 int64_t scale_stride_kb, const uint8_t* w1, const float* w1_scale, const uint8_t* w2,
@@ -410,6 +427,31 @@ int b200moe_run(const void* logits, int logits_dtype, const void* bias, int bias
   if (T == 0) return B200MOE_OK;
   int32_t* ids = ws.at<int32_t>(ws.L.topk_ids);
   float* w = ws.at<float>(ws.L.topk_w);
+  // Decode-size calls: routing, scan and placement in one block (B200MOE_FRONT=0: the separate kernels).
+  static const bool front_on = [] {
+    const char* v = getenv("B200MOE_FRONT");
+    return !(v && v[0] == '0');
+  }();
+  static const bool pairs_on = [] {
+    const char* v = getenv("B200MOE_GEMM");
+    return v && v[0] == 'p';
+  }();
+  if (front_on && !pairs_on && T <= kFrontSmallMaxTokens) {
+    if (!logits || !bias) return B200MOE_ERR_INVALID_ARGUMENT;
+    if ((logits_dtype != B200MOE_F32 && logits_dtype != B200MOE_BF16) ||
+        (bias_dtype != B200MOE_F32 && bias_dtype != B200MOE_BF16))
+      return B200MOE_ERR_INVALID_ARGUMENT;
+    if (local_expert_offset < 0 || local_expert_offset + e_local > kNumExperts) return B200MOE_ERR_INVALID_ARGUMENT;
+    int num_sms = 0;
+    if ((rc = ensure_device(&num_sms)) != B200MOE_OK) return rc;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if ((rc = clear_counters(ws, e_local, st)) != B200MOE_OK) return rc;
+    CUDA_TRY(launch_route_place_small(ws, logits, logits_dtype, bias, bias_dtype, T, routed_scaling_factor,
+                                      local_expert_offset, e_local, kTileM, st));
+    return experts_impl(ids, kTopK, w, kTopK, hidden_states, hidden_row_stride, hidden_scale, scale_stride_t,
+                        scale_stride_kb, w1, w1_scale, w2, w2_scale, T, e_local, local_expert_offset, hidden, inter,
+                        workspace, workspace_bytes, out_bf16, out_row_stride, stream, true);
+  }
   rc = b200moe_route(logits, logits_dtype, bias, bias_dtype, T, routed_scaling_factor, local_expert_offset, e_local,
                      hidden, inter, ids, w, workspace, workspace_bytes, stream);
   if (rc != B200MOE_OK) return rc;

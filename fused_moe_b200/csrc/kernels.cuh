@@ -14,10 +14,19 @@ cudaError_t launch_route(const void* logits, int logits_dtype, const void* bias,
 cudaError_t launch_count(const int32_t* ids, long long row_stride, int T, int local_off, int e_local,
                          int* chunk_counts, int num_sms, cudaStream_t stream);
 
+// `placed`: scan and place already ran (launch_route_place_small); only the gather is launched.
 cudaError_t launch_permute(const Workspace& ws, const int32_t* ids, long long ids_stride, const float* w,
                            long long w_stride, const uint8_t* hidden, long long hidden_row_stride,
                            const float* hscale, long long sstride_t, long long sstride_kb, int T, int e_local,
-                           int local_off, int hidden_dim, int pad_rows, int num_sms, cudaStream_t stream);
+                           int local_off, int hidden_dim, int pad_rows, int num_sms, cudaStream_t stream,
+                           bool placed = false);
+
+// Routing + scan + placement of at most kFrontSmallMaxTokens tokens in one block (front_small.cu);
+// writes the workspace's own topk_ids / topk_w.
+constexpr int kFrontSmallMaxTokens = 32;
+cudaError_t launch_route_place_small(const Workspace& ws, const void* logits, int logits_dtype, const void* bias,
+                                     int bias_dtype, int T, float rsf, int local_off, int e_local, int pad_rows,
+                                     cudaStream_t stream);
 
 // Decode GEMMs split the K range of a weight slab over up to kSplitKMax CTAs when a call has at
 // most kSplitKSlots (expert tile, slab) items, i.e. fewer than half of the SMs would stream weights.

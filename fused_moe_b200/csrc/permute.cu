@@ -160,14 +160,20 @@ gather_kernel(Workspace ws, const uint8_t* __restrict__ hidden, long long hidden
 cudaError_t launch_permute(const Workspace& ws, const int32_t* ids, long long ids_stride, const float* w,
                            long long w_stride, const uint8_t* hidden, long long hidden_row_stride,
                            const float* hscale, long long sstride_t, long long sstride_kb, int T, int e_local,
-                           int local_off, int hidden_dim, int pad_rows, int num_sms, cudaStream_t stream) {
+                           int local_off, int hidden_dim, int pad_rows, int num_sms, cudaStream_t stream,
+                           bool placed) {
   const int n_chunks = (T + kChunkTokens - 1) / kChunkTokens;
-  cudaError_t err = launch_chained(scan_kernel, dim3(1), dim3(256), 0, stream, ws, e_local, n_chunks, pad_rows);
-  if (err != cudaSuccess) return err;
-  if (n_chunks > 0) {
-    err = launch_chained(place_kernel, dim3(n_chunks), dim3(256), 0, stream, ws, ids, ids_stride, w, w_stride, T,
-                         local_off, e_local);
+  cudaError_t err = cudaSuccess;
+  if (!placed) {
+    err = launch_chained(scan_kernel, dim3(1), dim3(256), 0, stream, ws, e_local, n_chunks, pad_rows);
     if (err != cudaSuccess) return err;
+  }
+  if (n_chunks > 0) {
+    if (!placed) {
+      err = launch_chained(place_kernel, dim3(n_chunks), dim3(256), 0, stream, ws, ids, ids_stride, w, w_stride, T,
+                           local_off, e_local);
+      if (err != cudaSuccess) return err;
+    }
     long long cap_rows = ws.L.m_cap;
     int blocks = (int)((cap_rows + 7) / 8);
     int cap = num_sms * 8;
