@@ -61,13 +61,18 @@ requant_kernel(Workspace ws, int inter) {
 // `out[t] += bf16(G2 * w)` loop (experiments/fast_bench/correctness_bench.py:107-111).
 __global__ void __launch_bounds__(256)
 combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ tok_rows, int T, int hidden,
-               __nv_bfloat16* __restrict__ out, long long stride) {
+               __nv_bfloat16* __restrict__ out, long long stride, int splits) {
   chain_wait();
   chain_release();
   const int vec_per_row = hidden / 8;   // 8 bf16 = 16 bytes
   // One block per token (block-stride): the token's eight row numbers are sorted once per
-  // thread and then reused for all of the thread's 16-byte column groups.
-  for (int t = blockIdx.x; t < T; t += gridDim.x) {
+  // thread and then reused for all of the thread's 16-byte column groups.  Small batches cut a
+  // token's columns into `splits` parts on as many blocks, so that a thread has one group.
+  const int part_len = (vec_per_row + splits - 1) / splits;
+  for (int item = blockIdx.x; item < T * splits; item += gridDim.x) {
+    const int t = item / splits;
+    const int v_begin = (item % splits) * part_len;
+    const int v_end = min(vec_per_row, v_begin + part_len);
     int rows[kTopK];
     {
       const int4 a = reinterpret_cast<const int4*>(tok_rows + (size_t)t * kTopK)[0];
@@ -86,10 +91,10 @@ combine_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ tok_
     }
     uint4* dst = reinterpret_cast<uint4*>(out + (size_t)t * stride);
     if (rows[0] < 0) {   // no local expert took this token
-      for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) dst[v] = make_uint4(0u, 0u, 0u, 0u);
+      for (int v = v_begin + threadIdx.x; v < v_end; v += blockDim.x) dst[v] = make_uint4(0u, 0u, 0u, 0u);
       continue;
     }
-    for (int v = threadIdx.x; v < vec_per_row; v += blockDim.x) {
+    for (int v = v_begin + threadIdx.x; v < v_end; v += blockDim.x) {
       uint4 raw[kTopK];
 #pragma unroll
       for (int k = 0; k < kTopK; ++k)
@@ -152,12 +157,13 @@ cudaError_t launch_requant(const Workspace& ws, int inter, int num_sms, cudaStre
 cudaError_t launch_combine(const Workspace& ws, int T, int hidden, void* out_bf16, long long out_row_stride,
                            int num_sms, cudaStream_t stream) {
   if (T <= 0) return cudaSuccess;
-  int blocks = T;
+  const int splits = T < 2 * num_sms ? 4 : 1;
+  int blocks = T * splits;
   const int cap = num_sms * 8;   // 8 blocks of 256 threads are resident per SM
   if (blocks > cap) blocks = cap;
   return launch_chained(combine_kernel, dim3(blocks), dim3(256), 0, stream,
                         (const __nv_bfloat16*)ws.at<__nv_bfloat16>(ws.L.y), (const int*)ws.at<int>(ws.L.tok_rows), T,
-                        hidden, reinterpret_cast<__nv_bfloat16*>(out_bf16), out_row_stride);
+                        hidden, reinterpret_cast<__nv_bfloat16*>(out_bf16), out_row_stride, splits);
 }
 
 }  // namespace b200moe
