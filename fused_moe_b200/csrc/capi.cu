@@ -79,6 +79,7 @@ int ensure_device(int* num_sms) {
     CUDA_TRY(configure_grouped_gemm());
     CUDA_TRY(configure_grouped_gemm_pair());
     CUDA_TRY(configure_decode_gemm());
+    CUDA_TRY(configure_grouped_gemm_m256());
     g_dev[dev].ready = true;
   }
   *num_sms = g_dev[dev].num_sms;
@@ -171,6 +172,7 @@ void compute_layout(int T, int e_local, int hidden, int inter, b200moe_ws_layout
   L->topk_w = take((uint64_t)(T > 0 ? T : 1) * kTopK * 4);
   L->trace = take(2 * 8 * 64 * 8);   // B200MOE_PROF: absolute cycle stamps of CTA 0's first 64 K blocks
   L->splitk_scratch = take((uint64_t)kSplitKSlots * kSplitKMax * 16 * 128 * 4);   // 2 MiB
+  L->pair_tile = take((uint64_t)L->max_tiles * 4);
   L->total_bytes = off;
 }
 
@@ -326,15 +328,23 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
   }();
   int bn = use_pairs ? 256 : (nt ? 128 : ((long long)T * kTopK <= kSmallTileMaxPairs ? 128 : 256));
   if (!use_pairs && !nt && (bn_forced == 128 || bn_forced == 256)) bn = bn_forced;
+  // B200MOE_M256=1: 256-row items (two M tiles of an expert share each B box, gemm_m256.cu).  Off by default:
+  // measured 15-25 % slower than 128 x 256 items where experts hold one or two M tiles and equal where they
+  // hold many (a K block of either shape is bound by the same accumulator hand-off chain).
+  static const bool m256_on = [] {
+    const char* v = getenv("B200MOE_M256");
+    return v && v[0] == '1';
+  }();
+  const bool m256 = !nt && !use_pairs && bn_forced == 0 && m256_on;
 
   GemmParams g1;
   memset(&g1, 0, sizeof(g1));
   if ((rc = make_tmap(&g1.tmap_a, ws.base + ws.L.a_packed, (uint64_t)ws.L.m_cap, (uint64_t)hidden, (uint64_t)hidden,
-                      nt ? nt : kTileM)) != B200MOE_OK)
+                      nt ? nt : (m256 ? 2 * kTileM : kTileM))) != B200MOE_OK)
     return rc;
   if (use_pairs && (hidden % 256 != 0 || inter % 128 != 0)) return B200MOE_ERR_UNSUPPORTED_SHAPE;
-  if (!use_pairs)   // one box = bn/2 gate rows + the matching bn/2 up rows (decode kernels: 64 + 64)
-    rc = make_tmap_gate_up(&g1.tmap_b, w1, (uint64_t)e_local, (uint64_t)inter, (uint64_t)hidden, bn / 2);
+  if (!use_pairs)   // one box = bn/2 gate rows + the matching bn/2 up rows (decode and 256-row kernels: 64 + 64)
+    rc = make_tmap_gate_up(&g1.tmap_b, w1, (uint64_t)e_local, (uint64_t)inter, (uint64_t)hidden, m256 ? 64 : bn / 2);
   else
     rc = make_tmap(&g1.tmap_b, w1, (uint64_t)e_local * 2 * inter, (uint64_t)hidden, (uint64_t)hidden, bn / 2);
   if (rc != B200MOE_OK) return rc;
@@ -346,7 +356,8 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
   g1.m_cap = ws.L.m_cap;
   g1.n_per_expert = 2 * inter;
   g1.kblocks = hidden / kBlockK;
-  g1.n_tiles = nt ? inter / 64 : inter / (bn / 2);
+  g1.n_tiles = (nt || m256) ? inter / 64 : inter / (bn / 2);
+  g1.pair_tile = ws.at<int>(ws.L.pair_tile);
   g1.expert_count = ws.at<int>(ws.L.expert_count);
   g1.inter = inter;
   g1.hidden = hidden;
@@ -362,6 +373,7 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
   g1.trace = prof_on ? ws.at<unsigned long long>(ws.L.trace) : nullptr;
   if (g_prof_start) CUDA_TRY(cudaEventRecord(g_prof_start, st));
   if (nt) CUDA_TRY(launch_decode_gemm(1, nt, g1, num_sms, st));
+  else if (m256) CUDA_TRY(launch_grouped_gemm_m256(1, g1, num_sms, st));
   else if (use_pairs) CUDA_TRY(launch_grouped_gemm_pair(1, g1, num_sms, st));
   else CUDA_TRY(launch_grouped_gemm(1, bn, g1, num_sms, st));
   if (g_prof_stop) CUDA_TRY(cudaEventRecord(g_prof_stop, st));
@@ -372,10 +384,10 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
   GemmParams g2;
   memset(&g2, 0, sizeof(g2));
   if ((rc = make_tmap(&g2.tmap_a, ws.base + ws.L.act_q, (uint64_t)ws.L.m_cap, (uint64_t)inter, (uint64_t)inter,
-                      nt ? nt : kTileM)) != B200MOE_OK)
+                      nt ? nt : (m256 ? 2 * kTileM : kTileM))) != B200MOE_OK)
     return rc;
   if ((rc = make_tmap(&g2.tmap_b, w2, (uint64_t)e_local * hidden, (uint64_t)inter, (uint64_t)inter,
-                      !use_pairs ? bn : bn / 2)) != B200MOE_OK)   // the whole B tile (decode: the 128-row slab) in one box
+                      m256 ? 128 : (!use_pairs ? bn : bn / 2))) != B200MOE_OK)   // the whole B tile (decode: the 128-row slab) in one box
     return rc;
   g2.meta = g1.meta;
   g2.tile_expert = g1.tile_expert;
@@ -384,7 +396,8 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
   g2.m_cap = ws.L.m_cap;
   g2.n_per_expert = hidden;
   g2.kblocks = inter / kBlockK;
-  g2.n_tiles = nt ? hidden / 128 : hidden / bn;
+  g2.n_tiles = (nt || m256) ? hidden / 128 : hidden / bn;
+  g2.pair_tile = g1.pair_tile;
   g2.expert_count = g1.expert_count;
   g2.inter = inter;
   g2.hidden = hidden;
@@ -397,6 +410,7 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
   g2.prof = prof_on ? ws.at<unsigned long long>(ws.L.meta + 136) : nullptr;
   g2.trace = prof_on ? ws.at<unsigned long long>(ws.L.trace) + 8 * 64 : nullptr;
   if (nt) CUDA_TRY(launch_decode_gemm(2, nt, g2, num_sms, st));
+  else if (m256) CUDA_TRY(launch_grouped_gemm_m256(2, g2, num_sms, st));
   else if (use_pairs) CUDA_TRY(launch_grouped_gemm_pair(2, g2, num_sms, st));
   else CUDA_TRY(launch_grouped_gemm(2, bn, g2, num_sms, st));
 

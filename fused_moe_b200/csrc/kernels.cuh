@@ -40,6 +40,7 @@ struct GemmParams {
   CUtensorMap tmap_b;
   const int* meta;          // [0] = number of 128-row M tiles
   const int* tile_expert;   // expert of each M tile
+  const int* pair_tile;     // 256-row kernel: first M tile of each pair (meta[4] pairs)
   const int* row_token;     // token of each packed row, -1 for padding
   const int* expert_count;  // rows per local expert (decode kernel)
   const float* a_scale;     // GEMM1: [K/128][m_cap] activation scales
@@ -69,6 +70,10 @@ cudaError_t configure_grouped_gemm();   // opt-in shared memory sizes, once per 
 // The same GEMMs on CTA pairs (cta_group::2), tile 256 rows x 256 weight rows; segments must be padded to 256 rows.
 cudaError_t launch_grouped_gemm_pair(int mode, const GemmParams& p, int num_sms, cudaStream_t stream);
 cudaError_t configure_grouped_gemm_pair();
+
+// The same GEMMs with 256-row items on one CTA (gemm_m256.cu): pairs of M tiles of one expert share each B box.
+cudaError_t launch_grouped_gemm_m256(int mode, const GemmParams& p, int num_sms, cudaStream_t stream);
+cudaError_t configure_grouped_gemm_m256();
 
 // Decode sizes (T <= nt, nt 16 or 64): operands swapped, weights on the MMA's M side (gemm_decode.cu).
 cudaError_t launch_decode_gemm(int mode, int nt, const GemmParams& p, int num_sms, cudaStream_t stream);

@@ -51,6 +51,23 @@ scan_kernel(Workspace ws, int e_local, int n_chunks, int pad_rows) {
     __syncthreads();
   }
   int row0 = s_scan[e] - padded;
+  // pairs of consecutive M tiles of one expert (work items of the 256-row GEMM kernel)
+  const int pairs_e = (padded / kTileM + 1) / 2;
+  __syncthreads();
+  const int padded_total_all = s_scan[255];
+  __syncthreads();
+  s_scan[e] = pairs_e;
+  __syncthreads();
+  for (int off = 1; off < 256; off <<= 1) {
+    int v = e >= off ? s_scan[e - off] : 0;
+    __syncthreads();
+    s_scan[e] += v;
+    __syncthreads();
+  }
+  const int pair0 = s_scan[e] - pairs_e;
+  int* pair_tile = ws.at<int>(ws.L.pair_tile);
+  for (int j = 0; j < pairs_e; ++j) pair_tile[pair0 + j] = row0 / kTileM + 2 * j;
+  const int pairs_total = s_scan[255];
   int* expert_row0 = ws.at<int>(ws.L.expert_row0);
   int* expert_count = ws.at<int>(ws.L.expert_count);
   int* tile_expert = ws.at<int>(ws.L.tile_expert);
@@ -68,13 +85,14 @@ scan_kernel(Workspace ws, int e_local, int n_chunks, int pad_rows) {
   if (e < e_local && total) atomicAdd(&s_rows, total);
   __syncthreads();
   if (e == 0) {
-    int padded_total = s_scan[255];
+    int padded_total = padded_total_all;
     expert_row0[e_local] = padded_total;
     int* meta = ws.at<int>(ws.L.meta);
     meta[0] = padded_total / kTileM;
     meta[1] = padded_total;
     meta[2] = s_rows;
     meta[3] = pad_rows;
+    meta[4] = pairs_total;
   }
 }
 

@@ -54,3 +54,15 @@ def test_decode_sizes_with_separate_front_kernels():
                        env=env, cwd=ROOT, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
     assert "passed" in r.stdout
+
+
+@pytest.mark.gpu
+def test_small_shapes_stage_by_stage_with_256_row_items():
+    """B200MOE_M256=1 selects the kernel whose items are pairs of M tiles of one expert (off by default)."""
+    env = dict(os.environ, B200MOE_M256="1")
+    r = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu", "-k",
+                        "small_shapes or T64_ts0 or (oracle and 1024-0) or (oracle and 2048-0)",
+                        os.path.join(ROOT, "tests", "test_gpu_layer.py")],
+                       env=env, cwd=ROOT, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-2000:]
+    assert "passed" in r.stdout
