@@ -7,10 +7,10 @@
 // instead of (one M tile, 256 weight rows).  Per 128-wide K block the CTA still moves 48 KB
 // (A: 256 rows x 128 B in one box, B: 128 rows x 128 B) and runs 512 cycles of MMA, but only
 // 16 KB of that is weights, and an expert with up to 256 rows has every weight byte fetched
-// by exactly one SM.  That matters where the layer is a stream of weights out of HBM: one
-// SM draws ~50 GB/s from HBM at most (~27 B/clk), and with 128-row items the two M tiles of
-// a 130-250-row expert run on two SMs that both pull the same 32 KB of weights per K block
-// at miss latency, which is what bounds a K block at ~1250 cycles there.
+// by exactly one SM.  The idea it tests: where the layer is a stream of weights out of HBM,
+// one SM draws ~50 GB/s from HBM at most (~27 B/clk), and with 128-row items the two M tiles
+// of a 130-250-row expert run on two SMs that both pull the same 32 KB of weights per K block
+// at miss latency - close to that limit at the ~1250 cycles per K block measured there.
 //
 // Tensor memory: accumulator (m, b) = M tile m of the pair, K-block parity b, 128 columns each
 // (all 512 columns).  Issuer m (warp 1 + m) owns M tile m: four MMAs M=128, N=128 per K block
