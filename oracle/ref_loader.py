@@ -12,7 +12,9 @@ from __future__ import annotations
 import ast
 import os
 
-REFERENCE_ROOT = os.environ.get("FUSED_MOE_REFERENCE", "/root/reference")
+# FUSED_MOE_REFERENCE, or a checkout named "reference" beside this repository
+_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+REFERENCE_ROOT = os.environ.get("FUSED_MOE_REFERENCE", os.path.join(os.path.dirname(_REPO), "reference"))
 _REL = "experiments/fast_bench/correctness_bench.py"
 
 
