@@ -23,8 +23,11 @@ __device__ __forceinline__ uint32_t pack4_e4m3(float a, float b, float c, float 
   return lo | (hi << 16);
 }
 
-// One block per packed row (grid-stride): a row is 2-8 KB, so one warp walking it alone would
-// be a chain of dependent global loads; 256 threads fetch it in one or two rounds.
+// One block per group of four packed rows (grid-stride): a row is 2-8 KB, so one warp walking
+// it alone would be a chain of dependent global loads; 256 threads fetch a row in one or two
+// rounds, and four rows' loads are in flight together.
+constexpr int kRequantRows = 4;
+
 __global__ void __launch_bounds__(256)
 requant_kernel(Workspace ws, int inter) {
   chain_wait();
@@ -35,23 +38,36 @@ requant_kernel(Workspace ws, int inter) {
   const unsigned* row_amax = ws.at<unsigned>(ws.L.row_amax);
   uint8_t* act_q = ws.at<uint8_t>(ws.L.act_q);
   float* row_scale = ws.at<float>(ws.L.row_scale);
-  for (int m = blockIdx.x; m < rows; m += gridDim.x) {
-    if (row_token[m] < 0) continue;
-    const float amax = fmaxf(__uint_as_float(row_amax[m]), 1e-8f);
-    const float scale = fmaxf(amax / 448.0f, 1e-8f);
-    if (threadIdx.x == 0) row_scale[m] = scale;
-    const uint4* src = reinterpret_cast<const uint4*>(act + (size_t)m * inter);   // 8 halves
-    uint2* dst = reinterpret_cast<uint2*>(act_q + (size_t)m * inter);
-    for (int v = threadIdx.x; v < inter / 8; v += blockDim.x) {
-      const uint4 raw = src[v];
-      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
-      const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
-      const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&raw.z));
-      const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&raw.w));
-      uint2 pk;
-      pk.x = pack4_e4m3(a.x / scale, a.y / scale, b.x / scale, b.y / scale);
-      pk.y = pack4_e4m3(c.x / scale, c.y / scale, d.x / scale, d.y / scale);
-      dst[v] = pk;
+  const int vecs = inter / 8;   // 8 halves = 16 bytes
+  for (int m0 = blockIdx.x * kRequantRows; m0 < rows; m0 += gridDim.x * kRequantRows) {
+    float scale[kRequantRows];
+    bool live[kRequantRows];
+#pragma unroll
+    for (int r = 0; r < kRequantRows; ++r) {
+      const int m = m0 + r;
+      live[r] = m < rows && row_token[m] >= 0;
+      const float amax = live[r] ? fmaxf(__uint_as_float(row_amax[m]), 1e-8f) : 1.f;
+      scale[r] = fmaxf(amax / 448.0f, 1e-8f);
+      if (live[r] && threadIdx.x == 0) row_scale[m] = scale[r];
+    }
+    for (int v = threadIdx.x; v < vecs; v += blockDim.x) {
+      uint4 raw[kRequantRows];
+#pragma unroll
+      for (int r = 0; r < kRequantRows; ++r)
+        if (live[r]) raw[r] = reinterpret_cast<const uint4*>(act + (size_t)(m0 + r) * inter)[v];
+#pragma unroll
+      for (int r = 0; r < kRequantRows; ++r) {
+        if (!live[r]) continue;
+        const float sc = scale[r];
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw[r].x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw[r].y));
+        const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&raw[r].z));
+        const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&raw[r].w));
+        uint2 pk;
+        pk.x = pack4_e4m3(a.x / sc, a.y / sc, b.x / sc, b.y / sc);
+        pk.y = pack4_e4m3(c.x / sc, c.y / sc, d.x / sc, d.y / sc);
+        reinterpret_cast<uint2*>(act_q + (size_t)(m0 + r) * inter)[v] = pk;
+      }
     }
   }
 }
@@ -149,8 +165,9 @@ cudaError_t launch_wait_timeout_selftest(int* status, cudaStream_t stream) {
 }
 
 cudaError_t launch_requant(const Workspace& ws, int inter, int num_sms, cudaStream_t stream) {
-  long long cap_rows = ws.L.m_cap;
-  int blocks = (int)(cap_rows < (long long)num_sms * 16 ? cap_rows : (long long)num_sms * 16);
+  long long groups = (ws.L.m_cap + kRequantRows - 1) / kRequantRows;
+  int blocks = (int)(groups < (long long)num_sms * 8 ? groups : (long long)num_sms * 8);
+  if (blocks < 1) blocks = 1;
   return launch_chained(requant_kernel, dim3(blocks), dim3(256), 0, stream, ws, inter);
 }
 

@@ -96,7 +96,7 @@ scan_kernel(Workspace ws, int e_local, int n_chunks, int pad_rows) {
   }
 }
 
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 place_kernel(Workspace ws, const int32_t* __restrict__ ids, long long ids_stride,
              const float* __restrict__ w, long long w_stride, int T, int local_off, int e_local) {
   __shared__ int s_ids[kTopK][kChunkTokens];   // [k][token]: conflict-free when lanes walk tokens
@@ -188,7 +188,8 @@ cudaError_t launch_permute(const Workspace& ws, const int32_t* ids, long long id
   }
   if (n_chunks > 0) {
     if (!placed) {
-      err = launch_chained(place_kernel, dim3(n_chunks), dim3(256), 0, stream, ws, ids, ids_stride, w, w_stride, T,
+      // 32 warps per chunk: a call has few chunks, and a warp's walk over its experts is a chain of small loads
+      err = launch_chained(place_kernel, dim3(n_chunks), dim3(1024), 0, stream, ws, ids, ids_stride, w, w_stride, T,
                            local_off, e_local);
       if (err != cudaSuccess) return err;
     }
