@@ -83,20 +83,6 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return done;
 }
 
-// Non-blocking probe of an mbarrier phase (try_wait may suspend the thread for a while, and
-// waking it again adds latency to a hand-off that sits on the critical path).
-__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(done)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return done;
-}
-
 // Bounded wait on an mbarrier phase.  Returns false when the CTA is aborting (another
 // thread gave up) or when this wait ran out of budget; in the latter case the status word
 // in global memory receives the timeout code and `where` for diagnosis.
@@ -125,30 +111,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
                                           int* status, int where) {
   return mbar_wait_budget(bar, parity, abort_flag, status, where, kWaitBudgetCycles);
 }
-// Same contract, polling with test_wait: for the few waits whose wake-up latency is on the
-// critical path of the MMA / promotion hand-off.
-__device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                               int* status, int where) {
-  long long t0 = 0;
-  uint32_t spins = 0;
-  while (true) {
-    if (mbar_test_wait(bar, parity)) return true;
-    if (++spins >= 256u) {
-      spins = 0;
-      if (*abort_flag) return false;
-      long long now = clock64();
-      if (t0 == 0) {
-        t0 = now;
-      } else if (now - t0 > kWaitBudgetCycles) {
-        *abort_flag = 1;
-        if (atomicCAS(status + kStatusCode, 0, (int)B200MOE_ERR_DEVICE_TIMEOUT) == 0)
-          status[kStatusDetail] = where;
-        return false;
-      }
-    }
-  }
-}
-
 // TMA: 2D tiled load global -> shared, completion counted on an mbarrier.
 __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile(
