@@ -293,6 +293,12 @@ def run_b200_arm(args):
     t_wall1 = time.time()
     ms_total = ev0.elapsed_time(ev1)
 
+    if ep is not None and os.environ.get("B200MOE_EP_TRACE"):   # phase breakdown of one step, every rank, to stderr
+        out = step(logits, hq, hsc)
+        print(f"[rank {rank}] ep phases ms: " + json.dumps({k: round(v, 3) for k, v in ep.phase_ms().items()}) +
+              f" recv_rows {ep.last_recv_rows}", file=sys.stderr, flush=True)
+        barrier()
+
     # GEMM1 in place (separate short loop so that event creation stays out of the headline region)
     g1_ms = []
     for i in range(min(args.steps, 10)):

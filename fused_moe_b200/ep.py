@@ -22,6 +22,8 @@ from __future__ import annotations
 
 from typing import List, Optional
 
+import os
+
 import torch
 import torch.distributed as dist
 
@@ -122,6 +124,22 @@ class ExpertParallelMoE:
         self.ops = ops if ops is not None else CudaOps()
         self.last_recv_rows = 0
         self.last_send_counts: List[int] = []
+        # B200MOE_EP_TRACE=1: CUDA events at the phase boundaries of every forward; phase_ms() reads them
+        self._trace = bool(os.environ.get("B200MOE_EP_TRACE")) and isinstance(self.ops, CudaOps)
+        self._marks: list = []
+
+    def _mark(self, name: str):
+        if self._trace:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self._marks.append((name, ev))
+
+    def phase_ms(self) -> dict:
+        """Milliseconds between the phase marks of the last forward (synchronises the device)."""
+        if not self._marks:
+            return {}
+        torch.cuda.synchronize()
+        return {b[0]: a[1].elapsed_time(b[1]) for a, b in zip(self._marks[:-1], self._marks[1:])}
 
     def forward(self, routing_logits, routing_bias, hidden_states, hidden_states_scale,
                 w1, s1, w2, s2, routed_scaling_factor: float) -> torch.Tensor:
@@ -138,14 +156,18 @@ class ExpertParallelMoE:
                                                               hidden_states_scale, w1, s1, w2, s2,
                                                               routed_scaling_factor)
         dev = hidden_states.device
+        self._marks = []
+        self._mark("start")
         ids, w = ops.route(routing_logits, routing_bias, routed_scaling_factor, self.local_off,
                            self.e_local, hidden, inter)
         send_rows, dest_counts, send_slot = ops.pack(ids, w, hidden_states, hidden_states_scale, world)
 
         # counts: what I send to d  <->  what d will receive from me
+        self._mark("route_pack")
         recv_counts = torch.empty_like(dest_counts)
         dist.all_to_all_single(recv_counts, dest_counts, group=self.group)
         both = torch.stack([dest_counts, recv_counts]).cpu().tolist()    # one host read for both
+        self._mark("counts_exchange_and_host_read")
         send_n = [int(x) for x in both[0]]
         recv_n = [int(x) for x in both[1]]
         self.last_send_counts = send_n
@@ -158,14 +180,19 @@ class ExpertParallelMoE:
         dist.all_to_all_single(recv_rows[:n_recv], send_rows[:n_send], output_split_sizes=recv_n,
                                input_split_sizes=send_n, group=self.group)
 
+        self._mark("dispatch_all_to_all")
         # local experts over everything that arrived
         partial = ops.experts(recv_rows, n_recv, w1, s1, w2, s2, self.local_off, hidden, inter)
 
+        self._mark("local_experts")
         # combine: the same exchange backwards, bf16 rows
         returned = ops.empty((max(n_send, 1), hidden), torch.bfloat16, dev)
         dist.all_to_all_single(returned[:n_send], partial[:n_recv], output_split_sizes=send_n,
                                input_split_sizes=recv_n, group=self.group)
-        return ops.combine(returned, send_slot, dest_counts, T, hidden, world)
+        self._mark("return_all_to_all")
+        out = ops.combine(returned, send_slot, dest_counts, T, hidden, world)
+        self._mark("combine")
+        return out
 
     def _single(self, logits, bias, hs, hsc, w1, s1, w2, s2, rsf):
         ids, w = self.ops.route(logits, bias, rsf, 0, self.e_local, hs.shape[1], w2.shape[2])
