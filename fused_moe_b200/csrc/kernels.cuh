@@ -60,7 +60,7 @@ struct GemmParams {
   float* splitk_scratch;    // decode GEMMs: [kSplitKSlots][kSplitKMax][16][128] partial sums
   int* splitk_count;        // decode GEMMs: arrivals per weight slab, zero at kernel start and end
   unsigned long long* prof;   // optional cycle counters of CTA 0 (null: off)
-  unsigned long long* trace;  // optional [64][4] absolute cycle stamps of CTA 0's first K blocks
+  unsigned long long* trace;  // optional [64][8] absolute cycle stamps of CTA 0's first K blocks
 };
 
 // mode 1: GEMM1 + SwiGLU + row amax; mode 2: GEMM2 + weighted combine.  bn: 128 or 256.
