@@ -405,7 +405,10 @@ def run_b200_arm(args):
 
     h2d = sum(t.numel() * t.element_size() for t in host)
     d2h = out_host[0].numel() * out_host[0].element_size()
-    launches_per_step = kernel.launches_per_run(TOKENS_PER_RANK, e_local) if world == 1 else 12
+    # N > 1: route, plan + copy (pack), count, the 7 kernels of the local expert pipeline, combine;
+    # with the exchanges read from mapped peer memory one more (the ids pull)
+    launches_per_step = kernel.launches_per_run(TOKENS_PER_RANK, e_local) if world == 1 else \
+        (13 if ep.last_mode == "peer" else 12)
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -417,6 +420,7 @@ def run_b200_arm(args):
         "gpu_launches": launches_per_step * args.steps,
         "roofline": roof, "clocks": clocks,
         "rows_per_rank": [int(x) for x in allt[:, 3]],
+        "ep_exchange": (ep.last_mode if ep is not None else None),
     }
 
     if world == 1 and not args.no_sweep:

@@ -61,6 +61,9 @@ SIGNATURES = {
     "b200moe_launches_per_run": (_I, [_I, _I]),
     "b200moe_ep_pack": (_I, [_P, _P, _P, _L, _P, _L, _L, _I, _I, _I, _P, _P, _P, _P]),
     "b200moe_ep_combine": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),
+    "b200moe_ep_pull_ids": (_I, [_P, _P, _I, _L, _I, _P, _P, _P]),
+    "b200moe_experts_segments": (_I, [_P, _P, _P, _P, _I, _L, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _P, _L, _P]),
+    "b200moe_ep_combine_peers": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),
 }
 
 _lib = None

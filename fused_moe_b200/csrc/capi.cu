@@ -283,9 +283,13 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
                         int64_t scale_stride_t, int64_t scale_stride_kb, const uint8_t* w1, const float* w1_scale,
                         const uint8_t* w2, const float* w2_scale, int T, int e_local, int local_expert_offset,
                         int hidden, int inter, void* workspace, size_t workspace_bytes, void* out_bf16,
-                        int64_t out_row_stride, void* stream, bool placed) {
+                        int64_t out_row_stride, void* stream, bool placed, const RowSegments* segs = nullptr) {
   if (!topk_ids || !topk_w || !w1 || !w1_scale || !w2 || !w2_scale) return B200MOE_ERR_INVALID_ARGUMENT;
-  if (T > 0 && (!hidden_states || !hidden_scale || !out_bf16)) return B200MOE_ERR_INVALID_ARGUMENT;
+  if (T > 0 && ((!segs && (!hidden_states || !hidden_scale)) || !out_bf16)) return B200MOE_ERR_INVALID_ARGUMENT;
+  if (segs) {   // rows are read from the segments: no separate payload / scale arrays
+    hidden_row_stride = hidden;
+    hidden_states = nullptr;
+  }
   if (ids_row_stride < kTopK || w_row_stride < kTopK) return B200MOE_ERR_INVALID_ARGUMENT;
   if (local_expert_offset < 0 || local_expert_offset + e_local > kNumExperts) return B200MOE_ERR_INVALID_ARGUMENT;
   Workspace ws;
@@ -308,7 +312,7 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
   }();
   CUDA_TRY(launch_permute(ws, topk_ids, ids_row_stride, topk_w, w_row_stride, hidden_states, hidden_row_stride,
                           hidden_scale, scale_stride_t, scale_stride_kb, T, e_local, local_expert_offset, hidden,
-                          use_pairs ? 2 * kTileM : kTileM, num_sms, st, placed));
+                          use_pairs ? 2 * kTileM : kTileM, num_sms, st, placed, segs));
 
   // small problems get the narrower N tile: more work items to spread over the SMs
   // Up to 16 tokens: swapped-operand decode kernels (B200MOE_DECODE=0 turns them off; B200MOE_DECODE=64
@@ -510,6 +514,78 @@ int b200moe_ep_pack(const int32_t* topk_ids, const float* topk_w, const uint8_t*
   CUDA_TRY(launch_ep_pack(topk_ids, topk_w, hidden_states, hidden_row_stride, hidden_scale, scale_stride_t,
                           scale_stride_kb, T, hidden, world, send_rows, dest_counts, send_slot, num_sms,
                           reinterpret_cast<cudaStream_t>(stream)));
+  return B200MOE_OK;
+}
+
+namespace {
+int fill_segments(const void* const* seg_base, const int32_t* seg_rows, int n_segs, int64_t row_bytes, int hidden,
+                  RowSegments* segs, int* total_rows) {
+  if (!seg_base || !seg_rows || n_segs < 1 || n_segs > 8) return B200MOE_ERR_INVALID_ARGUMENT;
+  if (row_bytes < hidden + 4 * (hidden / kBlockK) + 64 || row_bytes % 16 != 0) return B200MOE_ERR_MISALIGNED;
+  memset(segs, 0, sizeof(*segs));
+  segs->n = n_segs;
+  segs->row_bytes = row_bytes;
+  int run = 0;
+  for (int s = 0; s < n_segs; ++s) {
+    if (seg_rows[s] < 0 || (seg_rows[s] > 0 && !seg_base[s])) return B200MOE_ERR_INVALID_ARGUMENT;
+    if (reinterpret_cast<uintptr_t>(seg_base[s]) % 16 != 0) return B200MOE_ERR_MISALIGNED;
+    segs->start[s] = run;
+    segs->base[s] = reinterpret_cast<const uint8_t*>(seg_base[s]);
+    run += seg_rows[s];
+  }
+  for (int s = n_segs; s < 9; ++s) segs->start[s] = run;
+  *total_rows = run;
+  return B200MOE_OK;
+}
+}  // namespace
+
+int b200moe_ep_pull_ids(const void* const* seg_base, const int32_t* seg_rows, int n_segs, int64_t row_bytes,
+                        int hidden, int32_t* topk_ids, float* topk_w, void* stream) {
+  RowSegments segs;
+  int rows = 0;
+  int rc = fill_segments(seg_base, seg_rows, n_segs, row_bytes, hidden, &segs, &rows);
+  if (rc != B200MOE_OK) return rc;
+  if (rows == 0) return B200MOE_OK;
+  if (!topk_ids || !topk_w) return B200MOE_ERR_INVALID_ARGUMENT;
+  int num_sms = 0;
+  if ((rc = ensure_device(&num_sms)) != B200MOE_OK) return rc;
+  CUDA_TRY(launch_ep_pull_ids(segs, rows, hidden, topk_ids, topk_w, num_sms, reinterpret_cast<cudaStream_t>(stream)));
+  return B200MOE_OK;
+}
+
+int b200moe_experts_segments(const int32_t* topk_ids, const float* topk_w, const void* const* seg_base,
+                             const int32_t* seg_rows, int n_segs, int64_t row_bytes, const uint8_t* w1,
+                             const float* w1_scale, const uint8_t* w2, const float* w2_scale, int e_local,
+                             int local_expert_offset, int hidden, int inter, void* workspace, size_t workspace_bytes,
+                             void* out_bf16, int64_t out_row_stride, void* stream) {
+  RowSegments segs;
+  int rows = 0;
+  int rc = fill_segments(seg_base, seg_rows, n_segs, row_bytes, hidden, &segs, &rows);
+  if (rc != B200MOE_OK) return rc;
+  return experts_impl(topk_ids, kTopK, topk_w, kTopK, nullptr, hidden, nullptr, 0, 0, w1, w1_scale, w2, w2_scale, rows,
+                      e_local, local_expert_offset, hidden, inter, workspace, workspace_bytes, out_bf16, out_row_stride,
+                      stream, false, &segs);
+}
+
+int b200moe_ep_combine_peers(const void* const* partial_bf16, const int32_t* row_start, const int32_t* send_slot,
+                             int T, int hidden, int world, void* out_bf16, void* stream) {
+  if (T < 0) return B200MOE_ERR_INVALID_ARGUMENT;
+  if (T == 0) return B200MOE_OK;
+  if (!partial_bf16 || !row_start || !send_slot || !out_bf16) return B200MOE_ERR_INVALID_ARGUMENT;
+  if (world != 1 && world != 2 && world != 4 && world != 8) return B200MOE_ERR_UNSUPPORTED_SHAPE;
+  if (hidden < 8 || hidden % 8 != 0) return B200MOE_ERR_UNSUPPORTED_SHAPE;
+  PeerPartials peers;
+  memset(&peers, 0, sizeof(peers));
+  for (int d = 0; d < world; ++d) {
+    if (!partial_bf16[d] || reinterpret_cast<uintptr_t>(partial_bf16[d]) % 16 != 0) return B200MOE_ERR_MISALIGNED;
+    peers.partial[d] = partial_bf16[d];
+  }
+  if (reinterpret_cast<uintptr_t>(out_bf16) % 16 != 0) return B200MOE_ERR_MISALIGNED;
+  int num_sms = 0;
+  int rc = ensure_device(&num_sms);
+  if (rc != B200MOE_OK) return rc;
+  CUDA_TRY(launch_ep_combine_peers(peers, row_start, send_slot, T, hidden, world, out_bf16, num_sms,
+                                   reinterpret_cast<cudaStream_t>(stream)));
   return B200MOE_OK;
 }
 

@@ -1,7 +1,9 @@
 // Expert-parallel helpers: build per-destination send rows, and sum the partial outputs
 // that come back.  The reference has no multi-GPU path (it only consumes
 // `local_expert_offset`, solution/python/kernel.py:591); rows travel between these two
-// kernels by NCCL all-to-all, always into the receiving GPU's own memory.
+// kernels by NCCL all-to-all into the receiving GPU's own memory, or - when the ranks' send and
+// partial buffers are mapped into each other's address space - are read in place by the
+// gather (permute.cu) and by ep_combine_peers_kernel with plain loads: no multicast anywhere.
 //
 // A token is sent at most once to each rank that owns one of its 8 experts; the send row
 // carries the e4m3 payload, its 1x128 scales and all 8 (id, weight) pairs, so the receiver
@@ -147,7 +149,84 @@ ep_combine_kernel(const __nv_bfloat16* __restrict__ returned, const int32_t* __r
   }
 }
 
+// ids + weights of every send row addressed to this rank, read where the sender packed them
+__global__ void __launch_bounds__(256)
+ep_pull_ids_kernel(RowSegments segs, int rows, int hidden_dim, int32_t* __restrict__ ids_out,
+                   float* __restrict__ w_out) {
+  const int trailer = hidden_dim + 4 * (hidden_dim / kBlockK);   // byte offset of ids[8] | weights[8]
+  const long long n = (long long)rows * 16;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i >> 4), j = (int)(i & 15);
+    const uint32_t v = reinterpret_cast<const uint32_t*>(segs.row(r) + trailer)[j];
+    if (j < 8) ids_out[(size_t)r * 8 + j] = (int32_t)v;
+    else w_out[(size_t)r * 8 + (j - 8)] = __uint_as_float(v);
+  }
+}
+
+// ep_combine_kernel with the return exchange folded in: each partial row is read from the
+// memory of the rank that produced it (plain loads over NVLink for a peer).
+__global__ void __launch_bounds__(256)
+ep_combine_peers_kernel(PeerPartials peers, const int32_t* __restrict__ row_start,
+                        const int32_t* __restrict__ send_slot, int T, int hidden_dim, int world,
+                        __nv_bfloat16* __restrict__ out) {
+  int start[kMaxWorld];
+#pragma unroll
+  for (int d = 0; d < kMaxWorld; ++d) start[d] = d < world ? row_start[d] : 0;
+  const int vec_per_row = hidden_dim / 8;   // 8 bf16 = 16 bytes
+  const long long n = (long long)T * vec_per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(i / vec_per_row), v = (int)(i % vec_per_row);
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+    for (int d = 0; d < kMaxWorld; ++d) {
+      if (d >= world) break;
+      const int slot = send_slot[(size_t)t * world + d];
+      if (slot < 0) continue;
+      const __nv_bfloat16* rows = reinterpret_cast<const __nv_bfloat16*>(peers.partial[d]);
+      const uint4 raw = reinterpret_cast<const uint4*>(rows + ((size_t)start[d] + slot) * hidden_dim)[v];
+      const __nv_bfloat162* p2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f = __bfloat1622float2(p2[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    uint4 pk;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) o2[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    reinterpret_cast<uint4*>(out + (size_t)t * hidden_dim)[v] = pk;
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_ep_pull_ids(const RowSegments& segs, int rows, int hidden_dim, int32_t* ids_out, float* w_out,
+                               int num_sms, cudaStream_t stream) {
+  if (rows <= 0) return cudaSuccess;
+  long long n = (long long)rows * 16;
+  int blocks = (int)((n + 255) / 256);
+  int cap = num_sms * 8;
+  if (blocks > cap) blocks = cap;
+  ep_pull_ids_kernel<<<blocks, 256, 0, stream>>>(segs, rows, hidden_dim, ids_out, w_out);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_ep_combine_peers(const PeerPartials& peers, const int32_t* row_start, const int32_t* send_slot,
+                                    int T, int hidden_dim, int world, void* out_bf16, int num_sms,
+                                    cudaStream_t stream) {
+  if (T <= 0) return cudaSuccess;
+  long long n = (long long)T * (hidden_dim / 8);
+  int blocks = (int)((n + 255) / 256);
+  int cap = num_sms * 16;
+  if (blocks > cap) blocks = cap;
+  ep_combine_peers_kernel<<<blocks, 256, 0, stream>>>(peers, row_start, send_slot, T, hidden_dim, world,
+                                                      reinterpret_cast<__nv_bfloat16*>(out_bf16));
+  return cudaGetLastError();
+}
 
 cudaError_t launch_ep_pack(const int32_t* ids, const float* w, const uint8_t* hidden, long long hidden_row_stride,
                            const float* hscale, long long sstride_t, long long sstride_kb, int T, int hidden_dim,

@@ -14,12 +14,30 @@ cudaError_t launch_route(const void* logits, int logits_dtype, const void* bias,
 cudaError_t launch_count(const int32_t* ids, long long row_stride, int T, int local_off, int e_local,
                          int* chunk_counts, int num_sms, cudaStream_t stream);
 
+// Rows that live in up to eight separate buffers (the send buffers of the ranks of an
+// expert-parallel group, this GPU's own or its peers' mapped memory): row r of the virtual
+// concatenation belongs to segment s with start[s] <= r < start[s+1] and sits at
+// base[s] + (r - start[s]) * row_bytes.  n == 0: not used.
+struct RowSegments {
+  int n;
+  int start[9];
+  const uint8_t* base[8];
+  long long row_bytes;
+  __host__ __device__ const uint8_t* row(int r) const {
+    int s = 0;
+#pragma unroll
+    for (int i = 1; i < 8; ++i)
+      if (i < n && r >= start[i]) s = i;
+    return base[s] + (size_t)(r - start[s]) * row_bytes;
+  }
+};
+
 // `placed`: scan and place already ran (launch_route_place_small); only the gather is launched.
 cudaError_t launch_permute(const Workspace& ws, const int32_t* ids, long long ids_stride, const float* w,
                            long long w_stride, const uint8_t* hidden, long long hidden_row_stride,
                            const float* hscale, long long sstride_t, long long sstride_kb, int T, int e_local,
                            int local_off, int hidden_dim, int pad_rows, int num_sms, cudaStream_t stream,
-                           bool placed = false);
+                           bool placed = false, const RowSegments* segs = nullptr);
 
 // Routing + scan + placement of at most kFrontSmallMaxTokens tokens in one block (front_small.cu);
 // writes the workspace's own topk_ids / topk_w.
@@ -89,6 +107,17 @@ cudaError_t launch_ep_pack(const int32_t* ids, const float* w, const uint8_t* hi
                            const float* hscale, long long sstride_t, long long sstride_kb, int T, int hidden_dim,
                            int world, uint8_t* send_rows, int32_t* dest_counts, int32_t* send_slot, int num_sms,
                            cudaStream_t stream);
+// ids + weights (the 64-byte trailer) of every row of `segs` into compact local arrays [rows][8]
+cudaError_t launch_ep_pull_ids(const RowSegments& segs, int rows, int hidden_dim, int32_t* ids_out, float* w_out,
+                               int num_sms, cudaStream_t stream);
+// ep_combine reading each destination's partial rows where they were produced: partial[d] is rank d's
+// (mapped) output buffer, row_start[d] (device) the first row of this rank's segment inside it
+struct PeerPartials {
+  const void* partial[8];
+};
+cudaError_t launch_ep_combine_peers(const PeerPartials& peers, const int32_t* row_start, const int32_t* send_slot,
+                                    int T, int hidden_dim, int world, void* out_bf16, int num_sms,
+                                    cudaStream_t stream);
 cudaError_t launch_ep_combine(const void* returned_bf16, const int32_t* send_slot, const int32_t* dest_counts, int T,
                               int hidden_dim, int world, void* out_bf16, int num_sms, cudaStream_t stream);
 

@@ -148,7 +148,8 @@ place_kernel(Workspace ws, const int32_t* __restrict__ ids, long long ids_stride
 
 __global__ void __launch_bounds__(256)
 gather_kernel(Workspace ws, const uint8_t* __restrict__ hidden, long long hidden_row_stride,
-              const float* __restrict__ hscale, long long sstride_t, long long sstride_kb, int hidden_dim) {
+              const float* __restrict__ hscale, long long sstride_t, long long sstride_kb, int hidden_dim,
+              RowSegments segs) {
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   chain_wait();
@@ -165,8 +166,18 @@ gather_kernel(Workspace ws, const uint8_t* __restrict__ hidden, long long hidden
     int t = row_token[m];
     if (t < 0) continue;
     if (lane == 0) row_amax[m] = 0u;   // GEMM1's epilogue takes the running maximum with atomicMax
-    const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)t * hidden_row_stride);
     uint4* dst = reinterpret_cast<uint4*>(a_packed + (size_t)m * hidden_dim);
+    if (segs.n > 0) {
+      // the row is a send row of some rank of the group (payload, then its scales), read where it was packed:
+      // plain loads from this GPU's or a peer's memory, so the dispatch and the gather are one pass
+      const uint8_t* row = segs.row(t);
+      const uint4* src = reinterpret_cast<const uint4*>(row);
+      for (int v = lane; v < vecs; v += 32) dst[v] = src[v];
+      const float* sc = reinterpret_cast<const float*>(row + hidden_dim);
+      for (int kb = lane; kb < kblocks; kb += 32) a_scale[(size_t)kb * m_cap + m] = sc[kb];
+      continue;
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(hidden + (size_t)t * hidden_row_stride);
     for (int v = lane; v < vecs; v += 32) dst[v] = __ldg(src + v);
     for (int kb = lane; kb < kblocks; kb += 32)
       a_scale[(size_t)kb * m_cap + m] = hscale[(size_t)t * sstride_t + (size_t)kb * sstride_kb];
@@ -179,7 +190,7 @@ cudaError_t launch_permute(const Workspace& ws, const int32_t* ids, long long id
                            long long w_stride, const uint8_t* hidden, long long hidden_row_stride,
                            const float* hscale, long long sstride_t, long long sstride_kb, int T, int e_local,
                            int local_off, int hidden_dim, int pad_rows, int num_sms, cudaStream_t stream,
-                           bool placed) {
+                           bool placed, const RowSegments* segs) {
   const int n_chunks = (T + kChunkTokens - 1) / kChunkTokens;
   cudaError_t err = cudaSuccess;
   if (!placed) {
@@ -197,8 +208,10 @@ cudaError_t launch_permute(const Workspace& ws, const int32_t* ids, long long id
     int blocks = (int)((cap_rows + 7) / 8);
     int cap = num_sms * 8;
     if (blocks > cap) blocks = cap;
+    RowSegments none;
+    none.n = 0;
     err = launch_chained(gather_kernel, dim3(blocks), dim3(256), 0, stream, ws, hidden, hidden_row_stride, hscale,
-                         sstride_t, sstride_kb, hidden_dim);
+                         sstride_t, sstride_kb, hidden_dim, segs ? *segs : none);
   }
   return err;
 }

@@ -14,9 +14,20 @@ exchanges around it.  Per call, on every rank:
   6. combine: NCCL all-to-all of the bf16 partial rows back to their sources;
   7. ``b200moe_ep_combine``: fp32 sum of a token's <= min(4, world) partial rows -> bf16.
 
-No kernel reads another GPU's memory; NVLink traffic is NCCL's.  The exchange logic is
-independent of the device: tests drive it over ``gloo`` with CPU stand-ins for the five
-device operations (``ops``), the product always uses ``CudaOps``.
+With NCCL ranks on one node the two bulk exchanges are folded into the kernels instead
+(``PeerExchange``): the send buffer and the partial-output buffer of every rank are
+symmetric-memory allocations mapped into every process, steps 4-5 become "pull the ids, then
+let the gather read payload and scales from the senders' buffers" (``b200moe_ep_pull_ids``,
+``b200moe_experts_segments``) and steps 6-7 become one kernel that sums the partial rows where
+they were produced (``b200moe_ep_combine_peers``): plain loads over NVLink, no multicast.  The
+two small NCCL all-to-alls that remain (row counts and offsets before, segment starts after the
+experts) are also what orders the ranks' kernels.  ``B200MOE_EP_P2P=0``, a ``gloo`` group or a
+failed mapping fall back to the NCCL path above; without the variable the mapped exchange is
+used by groups of two ranks (the size it has been run at), ``B200MOE_EP_P2P=1`` turns it on
+for 4 and 8.
+
+The exchange logic is independent of the device: tests drive it over ``gloo`` with CPU
+stand-ins for the five device operations (``ops``), the product always uses ``CudaOps``.
 """
 from __future__ import annotations
 
@@ -29,6 +40,10 @@ import torch.distributed as dist
 
 from . import _capi
 from . import kernel as _k
+
+# The mapped exchange buffers are only ever read with plain loads; keep torch from binding them to
+# an NVLink multicast object as well.
+os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
 E_GLOBAL = 256
 TOP_K = 8
@@ -45,7 +60,7 @@ class CudaOps:
     def route(self, logits, bias, rsf, local_off, e_local, hidden, inter):
         return _k.route(logits, bias, rsf, local_off, e_local, hidden, inter)
 
-    def pack(self, ids, w, hidden_states, hidden_scale, world):
+    def pack(self, ids, w, hidden_states, hidden_scale, world, send_buffer=None):
         dev = ids.device
         T, hidden = hidden_states.shape
         hs = _k._as_bytes(hidden_states, "hidden_states")
@@ -53,7 +68,11 @@ class CudaOps:
             hs = hs.contiguous()
         st_t, st_kb = _k._scale_strides(hidden_scale, T, hidden // BLOCK)
         rb = send_row_bytes(hidden)
-        send_rows = torch.empty((min(4, world) * max(T, 1), rb), dtype=torch.uint8, device=dev)
+        cap = min(4, world) * max(T, 1)
+        if send_buffer is not None and send_buffer.shape[0] >= cap and send_buffer.shape[1] == rb:
+            send_rows = send_buffer          # a symmetric-memory buffer that the peers read in place
+        else:
+            send_rows = torch.empty((cap, rb), dtype=torch.uint8, device=dev)
         dest_counts = torch.empty((world,), dtype=torch.int32, device=dev)
         send_slot = torch.empty((max(T, 1), world), dtype=torch.int32, device=dev)
         with torch.cuda.device(dev):
@@ -105,6 +124,24 @@ class CudaOps:
         return torch.empty(shape, dtype=dtype, device=device)
 
 
+class PeerExchange:
+    """Symmetric-memory buffers of one rank and their addresses in every rank (NCCL, one node)."""
+
+    def __init__(self, group, cap_tokens: int, hidden: int, world: int, dev):
+        """``cap_tokens``: the largest token count of any rank (the same number on every rank:
+        symmetric allocations have one size)."""
+        import torch.distributed._symmetric_memory as symm
+        rb = send_row_bytes(hidden)
+        self.cap_tokens, self.hidden = cap_tokens, hidden
+        self.send = symm.empty((min(4, world) * max(cap_tokens, 1), rb), dtype=torch.uint8, device=dev)
+        # every rank may send all of its tokens here
+        self.partial = symm.empty((world * max(cap_tokens, 1), hidden), dtype=torch.bfloat16, device=dev)
+        grp = group if group is not None else dist.group.WORLD
+        self.send_ptrs = [int(x) for x in symm.rendezvous(self.send, grp).buffer_ptrs]
+        self.partial_ptrs = [int(x) for x in symm.rendezvous(self.partial, grp).buffer_ptrs]
+        self.row_bytes = rb
+
+
 class ExpertParallelMoE:
     """One MoE layer whose experts are sharded over the ranks of ``group``.
 
@@ -113,7 +150,10 @@ class ExpertParallelMoE:
     layer output for them.
     """
 
-    def __init__(self, group: Optional[dist.ProcessGroup] = None, ops=None):
+    def __init__(self, group: Optional[dist.ProcessGroup] = None, ops=None, max_tokens: Optional[int] = None):
+        """``max_tokens``: capacity (tokens per rank) of the mapped exchange buffers; by default the
+        largest token count of any rank at the first call.  A later call with more tokens raises."""
+        self.max_tokens = max_tokens
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -127,6 +167,38 @@ class ExpertParallelMoE:
         # B200MOE_EP_TRACE=1: CUDA events at the phase boundaries of every forward; phase_ms() reads them
         self._trace = bool(os.environ.get("B200MOE_EP_TRACE")) and isinstance(self.ops, CudaOps)
         self._marks: list = []
+        self._peer: Optional[PeerExchange] = None
+        # B200MOE_EP_P2P: 1 = on, 0 = off; unset = on for two ranks, the only size this mode has been
+        # run at so far (larger groups keep NCCL until it has been)
+        p2p = os.environ.get("B200MOE_EP_P2P")
+        self._peer_failed = (p2p == "0") if p2p is not None else self.world != 2
+        self.last_mode = "single" if self.world == 1 else "nccl"
+
+    def _peer_exchange(self, T: int, hidden: int, dev) -> Optional[PeerExchange]:
+        """The mapped buffers for this problem size, or None when the NCCL path has to be used."""
+        if self._peer_failed or not isinstance(self.ops, CudaOps) or dev.type != "cuda":
+            return None
+        if dist.get_backend(self.group) != "nccl":
+            return None
+        if self._peer is None:           # first call: every rank gets here together
+            cap = self.max_tokens
+            if cap is None:
+                t_max = torch.tensor([T], dtype=torch.int32, device=dev)
+                dist.all_reduce(t_max, op=dist.ReduceOp.MAX, group=self.group)
+                cap = int(t_max.item())
+            ok = torch.ones(1, dtype=torch.int32, device=dev)
+            try:
+                self._peer = PeerExchange(self.group, cap, hidden, self.world, dev)
+            except Exception:            # no symmetric memory on this system: every rank must agree
+                ok.zero_()
+            dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+            if int(ok.item()) == 0:
+                self._peer, self._peer_failed = None, True
+                return None
+        if T > self._peer.cap_tokens or hidden != self._peer.hidden:
+            raise ValueError(f"{T} tokens of width {hidden} exceed the exchange buffers ({self._peer.cap_tokens} tokens "
+                             f"of width {self._peer.hidden}); pass max_tokens to ExpertParallelMoE")
+        return self._peer
 
     def _mark(self, name: str):
         if self._trace:
@@ -156,6 +228,11 @@ class ExpertParallelMoE:
                                                               hidden_states_scale, w1, s1, w2, s2,
                                                               routed_scaling_factor)
         dev = hidden_states.device
+        peer = self._peer_exchange(T, hidden, dev)
+        if peer is not None:
+            return self._forward_peer(peer, routing_logits, routing_bias, hidden_states, hidden_states_scale,
+                                      w1, s1, w2, s2, routed_scaling_factor)
+        self.last_mode = "nccl"
         self._marks = []
         self._mark("start")
         ids, w = ops.route(routing_logits, routing_bias, routed_scaling_factor, self.local_off,
@@ -193,6 +270,78 @@ class ExpertParallelMoE:
         out = ops.combine(returned, send_slot, dest_counts, T, hidden, world)
         self._mark("combine")
         return out
+
+    def _forward_peer(self, peer: PeerExchange, routing_logits, routing_bias, hidden_states, hidden_states_scale,
+                      w1, s1, w2, s2, rsf) -> torch.Tensor:
+        """The step with both bulk exchanges folded into the kernels (see the module docstring)."""
+        import ctypes as C
+        world, ops, me = self.world, self.ops, self.rank
+        T, hidden = hidden_states.shape
+        inter = w2.shape[2]
+        dev = hidden_states.device
+        lib = _capi.lib()
+        self.last_mode = "peer"
+        self._marks = []
+        self._mark("start")
+        ids, w = ops.route(routing_logits, routing_bias, rsf, self.local_off, self.e_local, hidden, inter)
+        send_rows, dest_counts, send_slot = ops.pack(ids, w, hidden_states, hidden_states_scale, world,
+                                                     send_buffer=peer.send)
+        self._mark("route_pack")
+        # to every destination: how many rows it gets from me and where they start in my send buffer.
+        # This exchange completes only after every rank's pack kernel: it is also what makes the
+        # send buffers safe to read.
+        seg_off = torch.cumsum(dest_counts, 0, dtype=torch.int32) - dest_counts
+        mine = torch.stack([dest_counts, seg_off], dim=1).contiguous()          # [world, 2]
+        theirs = torch.empty_like(mine)
+        dist.all_to_all_single(theirs, mine, group=self.group)
+        host = torch.cat([mine, theirs]).cpu().tolist()                         # one host read
+        send_n = [int(r[0]) for r in host[:world]]
+        recv_n = [int(r[0]) for r in host[world:]]
+        recv_off = [int(r[1]) for r in host[world:]]
+        self.last_send_counts = send_n
+        n_recv = sum(recv_n)
+        self.last_recv_rows = n_recv
+        self._mark("counts_exchange_and_host_read")
+
+        rb = peer.row_bytes
+        seg_base = (C.c_void_p * world)(*[peer.send_ptrs[s] + recv_off[s] * rb for s in range(world)])
+        seg_rows = (C.c_int32 * world)(*recv_n)
+        stream = torch.cuda.current_stream(dev).cuda_stream
+        if n_recv > 0:
+            r_ids = torch.empty((n_recv, TOP_K), dtype=torch.int32, device=dev)
+            r_w = torch.empty((n_recv, TOP_K), dtype=torch.float32, device=dev)
+            w1b, w2b = _k._as_bytes(w1, "gemm1_weights"), _k._as_bytes(w2, "gemm2_weights")
+            with torch.cuda.device(dev):
+                ws = _k.get_workspace(dev, n_recv, self.e_local, hidden, inter)
+                ws.last_T = n_recv
+                _capi.check(lib.b200moe_ep_pull_ids(seg_base, seg_rows, world, rb, hidden, r_ids.data_ptr(),
+                                                    r_w.data_ptr(), stream), "b200moe_ep_pull_ids")
+                _capi.check(lib.b200moe_count(r_ids.data_ptr(), TOP_K, n_recv, self.local_off, self.e_local, hidden,
+                                              inter, ws.ptr, ws.nbytes, stream), "b200moe_count")
+                _capi.check(lib.b200moe_experts_segments(
+                    r_ids.data_ptr(), r_w.data_ptr(), seg_base, seg_rows, world, rb,
+                    w1b.data_ptr(), s1.data_ptr(), w2b.data_ptr(), s2.data_ptr(), self.e_local, self.local_off,
+                    hidden, inter, ws.ptr, ws.nbytes, peer.partial.data_ptr(), hidden, stream),
+                    "b200moe_experts_segments")
+        self._mark("local_experts_reading_peers")
+
+        # to every source: where its segment starts in my partial buffer.  Enqueued after the expert
+        # kernels, so its completion on a rank means that every rank's partial rows are written.
+        starts, run = [], 0
+        for n in recv_n:
+            starts.append(run)
+            run += n
+        seg_start = torch.tensor(starts, dtype=torch.int32).to(dev, non_blocking=True)
+        row_start = torch.empty_like(seg_start)
+        dist.all_to_all_single(row_start, seg_start, group=self.group)
+        self._mark("segment_starts_exchange")
+        out = torch.empty((max(T, 1), hidden), dtype=torch.bfloat16, device=dev)
+        parts = (C.c_void_p * world)(*peer.partial_ptrs)
+        with torch.cuda.device(dev):
+            _capi.check(lib.b200moe_ep_combine_peers(parts, row_start.data_ptr(), send_slot.data_ptr(), T, hidden,
+                                                     world, out.data_ptr(), stream), "b200moe_ep_combine_peers")
+        self._mark("combine_reading_peers")
+        return out[:T]
 
     def _single(self, logits, bias, hs, hsc, w1, s1, w2, s2, rsf):
         ids, w = self.ops.route(logits, bias, rsf, 0, self.e_local, hs.shape[1], w2.shape[2])

@@ -220,6 +220,38 @@ B200MOE_API int b200moe_ep_combine(const void* returned_bf16, const int32_t* sen
                        const int32_t* dest_counts, int T, int hidden, int world,
                        void* out_bf16, void* stream);
 
+/* ---- the same exchange over mapped peer memory (NVLink loads inside the kernels instead of
+ * NCCL all-to-all; no counterpart in the reference) ----
+ * A "segment" s is the part of rank s's send buffer (b200moe_ep_pack layout) addressed to this
+ * rank: seg_base[s] points at its first row (this GPU's own memory or a peer's mapped into this
+ * process), seg_rows[s] is its row count; both arrays are HOST arrays of n_segs <= 8 entries.
+ * The virtual row order is segment 0, then segment 1, ...  The caller orders the kernels:
+ * the senders' pack kernels must have completed (e.g. the counts exchange between the ranks
+ * runs after them), and a sender must not repack before the readers are done. */
+
+/* ids and weights (the 64-byte trailer) of every segment row into compact [rows][8] arrays. */
+B200MOE_API int b200moe_ep_pull_ids(const void* const* seg_base, const int32_t* seg_rows, int n_segs,
+                        int64_t row_bytes, int hidden, int32_t* topk_ids, float* topk_w, void* stream);
+
+/* b200moe_experts whose gather reads payload and scales straight from the segments
+ * (dispatch and gather in one pass).  topk_ids / topk_w: the compact arrays of
+ * b200moe_ep_pull_ids; b200moe_count on them must have run.  out row r belongs to virtual row r. */
+B200MOE_API int b200moe_experts_segments(const int32_t* topk_ids, const float* topk_w,
+                        const void* const* seg_base, const int32_t* seg_rows, int n_segs, int64_t row_bytes,
+                        const uint8_t* w1, const float* w1_scale, const uint8_t* w2, const float* w2_scale,
+                        int e_local, int local_expert_offset, int hidden, int inter,
+                        void* workspace, size_t workspace_bytes,
+                        void* out_bf16, int64_t out_row_stride, void* stream);
+
+/* b200moe_ep_combine with the return exchange folded in: partial_bf16[d] (HOST array of `world`
+ * pointers) is rank d's output buffer of b200moe_experts_segments as mapped here, row_start[d]
+ * (DEVICE int32[world]) the first row of this rank's segment inside it.  The caller makes sure
+ * every rank's expert kernels have completed (e.g. the exchange that delivers row_start runs
+ * after them). */
+B200MOE_API int b200moe_ep_combine_peers(const void* const* partial_bf16, const int32_t* row_start,
+                        const int32_t* send_slot, int T, int hidden, int world,
+                        void* out_bf16, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

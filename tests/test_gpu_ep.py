@@ -73,6 +73,72 @@ def test_pack_experts_combine_with_emulated_ranks(world, T):
         assert frac_all >= 0.999, (world, r, frac_all, max_abs)
 
 
+@pytest.mark.parametrize("world,T", [(2, (70, 33)), (4, (40, 0, 129, 5)), (8, (9,) * 8)])
+def test_exchange_read_in_place_with_emulated_ranks(world, T):
+    """The peer-memory entry points with every rank's buffers on cuda:0: ids pulled from the senders'
+    buffers, the gather reading payload and scales there, and the combine reading the partial rows where
+    each expert rank wrote them - no copy between the "ranks" at all."""
+    import ctypes as C
+    from fused_moe_b200 import _capi
+    dev = torch.device("cuda", 0)
+    ops, lib = CudaOps(), _capi.lib()
+    per = 256 // world
+    rb = send_row_bytes(HIDDEN)
+    stream = torch.cuda.current_stream(dev).cuda_stream
+    all_w = synth.make_weights(256, 0, SEED, HIDDEN, INTER)
+    bias = synth.make_bias(SEED)
+    toks = [synth.make_tokens(T[r], r, SEED, HIDDEN) for r in range(world)]
+    packed = []
+    for r in range(world):
+        lg, hq, hsc = (t.to(dev) for t in toks[r])
+        ids, w = ops.route(lg, bias.to(dev), 2.5, r * per, per, HIDDEN, INTER)
+        rows, counts, slot = ops.pack(ids, w, hq, hsc, world)
+        torch.cuda.synchronize()
+        packed.append((rows, counts.cpu().numpy(), slot))
+    partials, starts = [], []          # per expert rank d: its output rows; start of each source's segment in it
+    for d in range(world):
+        recv_n = [int(packed[s][1][d]) for s in range(world)]
+        offs = [int(packed[s][1][:d].sum()) for s in range(world)]
+        n_recv = sum(recv_n)
+        starts.append([sum(recv_n[:s]) for s in range(world)])
+        seg_base = (C.c_void_p * world)(*[packed[s][0].data_ptr() + offs[s] * rb for s in range(world)])
+        seg_rows = (C.c_int32 * world)(*recv_n)
+        partial = torch.zeros((max(n_recv, 1), HIDDEN), dtype=torch.bfloat16, device=dev)
+        if n_recv:
+            r_ids = torch.empty((n_recv, 8), dtype=torch.int32, device=dev)
+            r_w = torch.empty((n_recv, 8), dtype=torch.float32, device=dev)
+            wd = tuple(t[d * per:(d + 1) * per].to(dev) for t in all_w)
+            w1b, w2b = K._as_bytes(wd[0], "gemm1_weights"), K._as_bytes(wd[2], "gemm2_weights")
+            ws = K.get_workspace(dev, n_recv, per, HIDDEN, INTER)
+            ws.last_T = n_recv
+            _capi.check(lib.b200moe_ep_pull_ids(seg_base, seg_rows, world, rb, HIDDEN, r_ids.data_ptr(),
+                                                r_w.data_ptr(), stream), "pull_ids")
+            _capi.check(lib.b200moe_count(r_ids.data_ptr(), 8, n_recv, d * per, per, HIDDEN, INTER, ws.ptr,
+                                          ws.nbytes, stream), "count")
+            _capi.check(lib.b200moe_experts_segments(
+                r_ids.data_ptr(), r_w.data_ptr(), seg_base, seg_rows, world, rb, w1b.data_ptr(),
+                wd[1].data_ptr(), w2b.data_ptr(), wd[3].data_ptr(), per, d * per, HIDDEN, INTER, ws.ptr, ws.nbytes,
+                partial.data_ptr(), HIDDEN, stream), "experts_segments")
+            torch.cuda.synchronize()
+            # the pulled ids are the senders' routing results, row for row
+            sent = torch.cat([packed[s][0][offs[s]:offs[s] + recv_n[s]] for s in range(world) if recv_n[s]])
+            trailer = HIDDEN + 4 * (HIDDEN // 128)
+            assert torch.equal(r_ids.cpu(), sent[:, trailer:trailer + 32].contiguous().view(torch.int32).cpu())
+        partials.append(partial)
+    for r in range(world):
+        if T[r] == 0:
+            continue
+        parts = (C.c_void_p * world)(*[p.data_ptr() for p in partials])
+        row_start = torch.tensor([starts[d][r] for d in range(world)], dtype=torch.int32, device=dev)
+        out = torch.empty((T[r], HIDDEN), dtype=torch.bfloat16, device=dev)
+        _capi.check(lib.b200moe_ep_combine_peers(parts, row_start.data_ptr(), packed[r][2].data_ptr(), T[r], HIDDEN,
+                                                 world, out.data_ptr(), stream), "combine_peers")
+        torch.cuda.synchronize()
+        ref = _oracle_full(toks[r], bias, all_w)
+        frac_all, frac_nz, max_abs = synth.check_close(out, ref["out"])
+        assert frac_all >= 0.999, (world, r, frac_all, max_abs)
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
@@ -81,8 +147,9 @@ def _free_port():
     return p
 
 
-def _nccl_worker(rank, world, port, tokens, ret):
+def _nccl_worker(rank, world, port, tokens, ret, p2p):
     import torch.distributed as dist
+    os.environ["B200MOE_EP_P2P"] = p2p
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -98,6 +165,7 @@ def _nccl_worker(rank, world, port, tokens, ret):
         for _ in range(2):          # twice: buffers and workspaces are reused
             out = ep.forward(lg, synth.make_bias(SEED).to(dev), hq, hsc, *w, 2.5)
         torch.cuda.synchronize()
+        ret["mode%d" % rank] = ep.last_mode
         ret[rank] = out.cpu().view(torch.int16).numpy().copy()
         dist.barrier()
     finally:
@@ -105,12 +173,16 @@ def _nccl_worker(rank, world, port, tokens, ret):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_nccl_exchange_on_two_gpus_matches_single_rank_oracle():
+@pytest.mark.parametrize("p2p", ["1", "0"])
+def test_nccl_exchange_on_two_gpus_matches_single_rank_oracle(p2p):
+    """p2p=1: the bulk exchanges are loads from mapped peer memory inside the gather and combine kernels
+    (falls back to NCCL where symmetric memory is unavailable); p2p=0: NCCL all-to-all."""
     import torch.multiprocessing as mp
     world, tokens = 2, (300, 77)
     mgr = mp.get_context("spawn").Manager()
     ret = mgr.dict()
-    mp.spawn(_nccl_worker, args=(world, _free_port(), tokens, ret), nprocs=world, join=True)
+    mp.spawn(_nccl_worker, args=(world, _free_port(), tokens, ret, p2p), nprocs=world, join=True)
+    assert ret["mode0"] == ret["mode1"] and (p2p == "1" or ret["mode0"] == "nccl"), dict(ret).get("mode0")
     all_w = synth.make_weights(256, 0, SEED, HIDDEN, INTER)
     bias = synth.make_bias(SEED)
     for r in range(world):
