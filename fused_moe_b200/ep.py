@@ -22,9 +22,8 @@ let the gather read payload and scales from the senders' buffers" (``b200moe_ep_
 they were produced (``b200moe_ep_combine_peers``): plain loads over NVLink, no multicast.  The
 two small NCCL all-to-alls that remain (row counts and offsets before, segment starts after the
 experts) are also what orders the ranks' kernels.  ``B200MOE_EP_P2P=0``, a ``gloo`` group or a
-failed mapping fall back to the NCCL path above; without the variable the mapped exchange is
-used by groups of two ranks (the size it has been run at), ``B200MOE_EP_P2P=1`` turns it on
-for 4 and 8.
+failed mapping fall back to the NCCL path above.  Both forms give bit-identical outputs
+(tests/test_gpu_ep.py, 2, 4 and 8 GPUs).
 
 The exchange logic is independent of the device: tests drive it over ``gloo`` with CPU
 stand-ins for the five device operations (``ops``), the product always uses ``CudaOps``.
@@ -168,10 +167,7 @@ class ExpertParallelMoE:
         self._trace = bool(os.environ.get("B200MOE_EP_TRACE")) and isinstance(self.ops, CudaOps)
         self._marks: list = []
         self._peer: Optional[PeerExchange] = None
-        # B200MOE_EP_P2P: 1 = on, 0 = off; unset = on for two ranks, the only size this mode has been
-        # run at so far (larger groups keep NCCL until it has been)
-        p2p = os.environ.get("B200MOE_EP_P2P")
-        self._peer_failed = (p2p == "0") if p2p is not None else self.world != 2
+        self._peer_failed = os.environ.get("B200MOE_EP_P2P", "1") == "0"
         self.last_mode = "single" if self.world == 1 else "nccl"
 
     def _peer_exchange(self, T: int, hidden: int, dev) -> Optional[PeerExchange]:

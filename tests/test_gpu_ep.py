@@ -172,6 +172,60 @@ def _nccl_worker(rank, world, port, tokens, ret, p2p):
         dist.destroy_process_group()
 
 
+def _both_forms_worker(rank, world, port, tokens, ret):
+    """Both exchange forms in one process group: the outputs must be bit-identical (same partial rows,
+    summed in the same order)."""
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        per = 256 // world
+        w = synth.make_weights(per, rank * per, SEED, HIDDEN, INTER, device=dev)
+        lg, hq, hsc = (t.to(dev) for t in synth.make_tokens(tokens[rank], rank, SEED, HIDDEN))
+        bias = synth.make_bias(SEED).to(dev)
+        outs, modes = [], []
+        for p2p in ("1", "0"):
+            os.environ["B200MOE_EP_P2P"] = p2p
+            ep = ExpertParallelMoE()
+            for _ in range(2):
+                out = ep.forward(lg, bias, hq, hsc, *w, 2.5)
+            torch.cuda.synchronize()
+            outs.append(out.clone())
+            modes.append(ep.last_mode)
+            dist.barrier()
+        ret[rank] = (modes, bool(torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))),
+                     outs[0].cpu().view(torch.int16).numpy().copy())
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_both_exchange_forms_agree_bit_for_bit_and_match_the_oracle(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    tokens = tuple([300, 77, 129, 0, 64, 5, 200, 31][:world])
+    mgr = mp.get_context("spawn").Manager()
+    ret = mgr.dict()
+    mp.spawn(_both_forms_worker, args=(world, _free_port(), tokens, ret), nprocs=world, join=True)
+    all_w = synth.make_weights(256, 0, SEED, HIDDEN, INTER)
+    bias = synth.make_bias(SEED)
+    for r in range(world):
+        modes, same, bits = ret[r]
+        assert modes[1] == "nccl" and modes[0] in ("peer", "nccl"), modes
+        assert same, f"rank {r}: the two exchange forms differ"
+        if tokens[r] == 0:
+            continue
+        ref = _oracle_full(synth.make_tokens(tokens[r], r, SEED, HIDDEN), bias, all_w)
+        got = torch.from_numpy(bits).view(torch.bfloat16)
+        frac_all, frac_nz, max_abs = synth.check_close(got, ref["out"])
+        assert frac_all >= 0.999, (r, frac_all, max_abs)
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
 @pytest.mark.parametrize("p2p", ["1", "0"])
 def test_nccl_exchange_on_two_gpus_matches_single_rank_oracle(p2p):
