@@ -14,12 +14,13 @@ tokens in pinned host memory and the bf16 result copied back, inside the timed r
 steps overlap the kernels of the current one (two slots, two copy streams).
 
 Extra objects on the line: `roofline` (GEMM1, the dominant kernel, timed in place with
-CUDA events through b200moe_profile_next_gemm1), `cpu_baseline` (the numpy oracle on the
-host cores over a bounded sample), `clocks` (nvidia-smi samples during the timed region)
+CUDA events through b200moe_profile_next_gemm1), `cpu_baseline` (the reference's torch function
+on the host cores over a bounded sample), `clocks` (nvidia-smi samples during the timed region)
 and, at N=1, `sweep`: the 32-local-expert slice at T = 1..16384 with per-T microseconds
 and roofline fractions (L2 flushed between iterations).
 
---impl reference times the CPU oracle port alone (rank 0 only under torchrun).
+--impl reference times the reference project's own torch function on the host cores alone
+(rank 0 only under torchrun), one 32-expert slice of the layer per step.
 """
 from __future__ import annotations
 
@@ -112,64 +113,49 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------------------
-# CPU arm: the oracle port on the host cores, bounded sample
+# CPU arm: the reference's own torch function on the host cores, one 32-expert slice per step
 # ----------------------------------------------------------------------------------------
+SLICE_EXPERTS = 32
+N_SLICES = 256 // SLICE_EXPERTS
 
-def cpu_sample(tokens, bias, expert_loader, n_experts_total, budget_s, max_experts=None):
-    """Runs the oracle port on all tokens of one rank through a sample of the experts and
-    extrapolates to the whole layer.  Experts are visited in a fixed scattered order
-    (e = 37*i mod 256); dequantisation (a per-expert cost) and the row work (GEMM1, SwiGLU,
-    requant, GEMM2, combine: a per-row cost) are timed apart, and the whole-layer time is
-    front + per-expert cost * active experts + per-row cost * rows of the full routing.
-    Returns (tokens/s, description, experts visited)."""
-    from oracle import moe_oracle as O
+
+def host_threads() -> int:
+    """All host cores for torch's intra-op pool, whatever OMP_NUM_THREADS the launcher exported
+    (torch.distributed.run sets it to 1); returns the thread count actually in use."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    return torch.get_num_threads()
+
+
+def load_cpu_function():
+    """(callable with the ten reference arguments -> bf16 [T, hidden], kind).  kind "reference":
+    the reference project's own `_reference_impl` (from its checkout, or the copy that
+    oracle/make_ref.py extracted into oracle/_ref/); kind "port": the numpy/torch restatement."""
+    from oracle import ref_loader
+    if ref_loader.available():
+        return ref_loader.load_reference_impl(), "reference", ref_loader.source()
+    from oracle import moe_oracle
+
+    def port(*args):
+        return moe_oracle.moe_layer_torch(*args)["out"]
+    return port, "port", "oracle/moe_oracle.py"
+
+
+def cpu_slice_seconds(fn, tokens, bias, weights, slice_idx):
+    """One call of the CPU function: all tokens of one rank, experts [32 s, 32 s + 32)."""
     logits, hq, hsc = tokens
-    T = logits.shape[0]
     t0 = time.perf_counter()
-    ids, w, _, _ = O.route(logits.numpy(), bias.float().numpy(), RSF)
-    x = O.dequant_rows(hq.view(torch.uint8).numpy(), O.hidden_scale_rows(hsc.numpy(), T, HIDDEN // 128))
-    t_front = time.perf_counter() - t0
-    counts = O.local_counts(ids, 0, n_experts_total)
-    done, rows, t_deq, t_rows = 0, 0, 0.0, 0.0
-    out = np.zeros((T, HIDDEN), dtype=np.float32)
-    while done < n_experts_total and (t_deq + t_rows < budget_s or done == 0):
-        if max_experts is not None and done >= max_experts:
-            break
-        e = (37 * done) % n_experts_total
-        w1q, s1, w2q, s2 = expert_loader(e)
-        t1 = time.perf_counter()
-        w1 = O.dequant_blocks(w1q, s1)
-        w2 = O.dequant_blocks(w2q, s2)
-        t2 = time.perf_counter()
-        hit = ids == e
-        sel = np.nonzero(hit.any(axis=1))[0]
-        if sel.size:
-            act = O.swiglu(x[sel] @ w1.T)
-            q, scale = O.requant_rows(act)
-            g2 = (O.e4m3_decode(q) * scale[:, None]).astype(np.float32) @ w2.T
-            wk = w[sel, hit[sel].argmax(axis=1)]
-            out[sel] = O.round_bf16(out[sel] + O.round_bf16(g2 * wk[:, None]))
-            rows += sel.size
-        t3 = time.perf_counter()
-        t_deq += t2 - t1
-        t_rows += t3 - t2
-        done += 1
-    n_active = int((counts > 0).sum())
-    est = t_front + t_deq / max(done, 1) * n_active + t_rows / max(rows, 1) * int(counts.sum())
-    desc = (f"all {T} tokens of one rank through {done} of {n_experts_total} experts (scattered ids, {rows} of "
-            f"{int(counts.sum())} expert rows, {t_front + t_deq + t_rows:.1f} s of CPU work); whole layer = front "
-            f"{t_front:.2f} s + {t_deq / max(done, 1):.3f} s/expert x {n_active} + "
-            f"{1e3 * t_rows / max(rows, 1):.3f} ms/row x {int(counts.sum())}")
-    return T / est, desc, done
+    fn(logits, bias, hq, hsc, *weights, SLICE_EXPERTS * slice_idx, RSF)
+    return time.perf_counter() - t0
 
 
-def make_expert_loader_cpu():
-    from fused_moe_b200 import synth
-
-    def load(e):
-        q1, s1, q2, s2 = synth.make_expert(e, 0)
-        return (q1.view(torch.uint8).numpy(), s1.numpy(), q2.view(torch.uint8).numpy(), s2.numpy())
-    return load
+def cpu_sample_text(kind, src, n_calls, secs, same_weights):
+    return (f"each step = the {'reference project' if kind == 'reference' else 'port'}'s torch function "
+            f"({src}) on all {TOKENS_PER_RANK} tokens of rank 0 for one 32-expert slice "
+            f"(local_expert_offset = 32 * (step mod 8)); 8 consecutive steps cover every (token, expert) pair of "
+            f"the 256-expert layer once, so tokens/s = {TOKENS_PER_RANK} / (8 * mean step time); {n_calls} slice "
+            f"calls timed, {secs:.1f} s of CPU work"
+            + ("; the slices reuse one set of 32 experts' weight bytes (routing, rows and shapes are each "
+               "slice's own)" if same_weights else ""))
 
 
 def run_reference_arm(args):
@@ -177,38 +163,28 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
+    cores = host_threads()
+    fn, kind, src = load_cpu_function()
     tokens = synth.make_tokens(TOKENS_PER_RANK, 0, 0)
     bias = synth.make_bias(0)
-    loader = make_expert_loader_cpu()
-    cache = {}
-
-    def cached(e):
-        if e not in cache:
-            cache[e] = loader(e)
-        return cache[e]
-    # calibrate on one expert, then size a step so that the whole run stays within a few minutes
-    t0 = time.perf_counter()
-    cpu_sample(tokens, bias, cached, 256, 0.0, max_experts=1)
-    one = time.perf_counter() - t0
-    per_step_budget = max(2.0, min(20.0, 150.0 / max(args.steps + args.warmup, 1)))
-    n_exp = int(max(1, min(256, per_step_budget / max(one, 1e-3))))
-    for i in range(n_exp):
-        cached((37 * i) % 256)
-    vals, desc = [], ""
+    weights = synth.make_weights(SLICE_EXPERTS, 0, 0)   # ~20 s; reused by every slice (timing only)
+    times = []
     for i in range(args.warmup + args.steps):
-        v, desc, _ = cpu_sample(tokens, bias, cached, 256, 1e9, max_experts=n_exp)
+        t = cpu_slice_seconds(fn, tokens, bias, weights, i % N_SLICES)
         if i >= args.warmup:
-            vals.append(v)
-    value = statistics.median(vals)
+            times.append(t)
+    mean_s = statistics.mean(times)
+    value = TOKENS_PER_RANK / (N_SLICES * mean_s)
+    whole = sum(times[:N_SLICES]) if len(times) >= N_SLICES else None
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * TOKENS_PER_RANK / value,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1000.0 * mean_s,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic (seeded generators, contest shapes)",
         "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": kind,
+                         "sample": cpu_sample_text(kind, src, len(times), sum(times), True),
+                         "whole_pass_s_measured": whole, "whole_pass_s_from_mean": N_SLICES * mean_s},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -424,16 +400,26 @@ def run_b200_arm(args):
     }
 
     if world == 1 and not args.no_sweep:
-        line["sweep"] = sweep(kernel, synth, dev, bias, (w1, s1, w2, s2), peaks)
+        cpu_fn = None
+        if not args.no_cpu:
+            host_threads()
+            cpu_fn = load_cpu_function()[0]
+        line["sweep"] = sweep(kernel, synth, dev, bias, (w1, s1, w2, s2), peaks, cpu_fn)
+    if world == 1 and not args.no_yardstick:
+        del out
+        torch.cuda.empty_cache()
+        line["yardstick"] = run_yardstick()
     if world == 1 and not args.no_cpu:
-        cores = os.cpu_count() or 1
-        torch.set_num_threads(cores)
-
-        def gpu_loader(e):
-            u8 = lambda t: t.view(torch.uint8).cpu().numpy()
-            return u8(w1[e]), s1[e].cpu().numpy(), u8(w2[e]), s2[e].cpu().numpy()
-        v, desc, _ = cpu_sample((logits_c, hq_c, hsc_c), bias.cpu(), gpu_loader, 256, args.cpu_budget)
-        line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": "port", "sample": desc}
+        cores = host_threads()
+        fn, kind, src = load_cpu_function()
+        times, sl = [], 0
+        while sl < N_SLICES and (sum(times) < args.cpu_budget or not times):
+            wsl = tuple(t[sl * SLICE_EXPERTS:(sl + 1) * SLICE_EXPERTS].cpu() for t in (w1, s1, w2, s2))
+            times.append(cpu_slice_seconds(fn, (logits_c, hq_c, hsc_c), bias.cpu(), wsl, sl))
+            sl += 1
+        v = TOKENS_PER_RANK / (N_SLICES * statistics.mean(times))
+        line["cpu_baseline"] = {"value": v, "unit": UNIT, "cores": cores, "kind": kind,
+                                "sample": cpu_sample_text(kind, src, len(times), sum(times), False)}
     elif not args.no_cpu:
         line["cpu_baseline"] = None
     print(json.dumps(line), flush=True)
@@ -442,16 +428,27 @@ def run_b200_arm(args):
         dist.destroy_process_group()
 
 
-def sweep(kernel, synth, dev, bias, weights, peaks):
-    """32-local-expert slice (experts 0..31) at the decode and prefill token counts."""
+# (tokens, token seed, Zipf bias): BASELINE configs 1 (T = 8), 2 (decode, two token seeds per T that give
+# at least one local row where such a seed exists), 3 (prefill) and 5 (Zipf load imbalance, T = 2048)
+SWEEP_CASES = ((1, 2, False), (1, 1, False), (4, 1, False), (4, 2, False), (8, 0, False), (16, 0, False),
+               (16, 1, False), (64, 0, False), (64, 1, False), (1024, 0, False), (4096, 0, False),
+               (16384, 0, False), (2048, 0, True))
+
+
+def sweep(kernel, synth, dev, bias, weights, peaks, cpu_fn=None):
+    """32-local-expert slice (experts 0..31) at the decode, prefill and Zipf token counts; with `cpu_fn`
+    (the reference's torch function) each row also carries its CPU time on the host cores."""
     w1, s1, w2, s2 = (t[:32] for t in weights)
+    w_cpu = tuple(t.cpu() for t in (w1, s1, w2, s2)) if cpu_fn is not None else None
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device=dev)
     fp8_peak = 2.0 * peaks["bf16_tflops"]
     rows = []
-    for T, tseed in ((1, 2), (4, 1), (16, 0), (64, 0), (1024, 0), (4096, 0), (16384, 0)):
-        lg, hq, hsc = (t.to(dev) for t in synth.make_tokens(T, 0, tseed))
+    for T, tseed, zipf in SWEEP_CASES:
+        lg_c, hq_c, hsc_c = synth.make_tokens(T, 0, tseed)
+        lg, hq, hsc = (t.to(dev) for t in (lg_c, hq_c, hsc_c))
+        b = synth.make_bias(0, zipf=True).to(dev) if zipf else bias
         for _ in range(3):
-            kernel.custom_kernel(lg, bias, hq, hsc, w1, s1, w2, s2, 0, RSF)
+            kernel.custom_kernel(lg, b, hq, hsc, w1, s1, w2, s2, 0, RSF)
         torch.cuda.synchronize()
         ws = kernel.get_workspace(dev, T, 32, HIDDEN, INTER)
         meta = ws.view("meta", torch.int32, (8,)).cpu().numpy()
@@ -460,21 +457,42 @@ def sweep(kernel, synth, dev, bias, weights, peaks):
         ts = []
         for _ in range(10):
             flush.zero_()
-            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a.record()
-            kernel.custom_kernel(lg, bias, hq, hsc, w1, s1, w2, s2, 0, RSF)
-            b.record()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            kernel.custom_kernel(lg, b, hq, hsc, w1, s1, w2, s2, 0, RSF)
+            e1.record()
             torch.cuda.synchronize()
-            ts.append(a.elapsed_time(b))
+            ts.append(e0.elapsed_time(e1))
         us = statistics.median(ts) * 1000.0
         nbytes = synth.algorithmic_bytes(T, n_active)
         flops = synth.algorithmic_flops(m_local)
-        rows.append({"T": T, "token_seed": tseed, "us": us, "tokens_per_s": T / (us * 1e-6), "rows": m_local,
-                     "active_experts": n_active,
-                     "hbm_gbs": nbytes / (us * 1e-6) / 1e9, "hbm_frac": nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"],
-                     "fp8_tflops": flops / (us * 1e-6) / 1e12, "fp8_frac": flops / (us * 1e-6) / 1e12 / fp8_peak,
-                     "bound": "hbm" if nbytes / (peaks["hbm_gbs"] * 1e9) >= flops / (fp8_peak * 1e12) else "tensor"})
+        row = {"T": T, "token_seed": tseed, "zipf": zipf, "us": us, "tokens_per_s": T / (us * 1e-6),
+               "rows": m_local, "active_experts": n_active,
+               "hbm_gbs": nbytes / (us * 1e-6) / 1e9, "hbm_frac": nbytes / (us * 1e-6) / 1e9 / peaks["hbm_gbs"],
+               "fp8_tflops": flops / (us * 1e-6) / 1e12, "fp8_frac": flops / (us * 1e-6) / 1e12 / fp8_peak,
+               "bound": "hbm" if nbytes / (peaks["hbm_gbs"] * 1e9) >= flops / (fp8_peak * 1e12) else "tensor"}
+        if cpu_fn is not None:
+            t0 = time.perf_counter()
+            cpu_fn(lg_c, b.cpu(), hq_c, hsc_c, *w_cpu, 0, RSF)
+            row["cpu_s"] = time.perf_counter() - t0
+        rows.append(row)
     return rows
+
+
+def run_yardstick():
+    """The reference's own CUDA solution on the same GPU and inputs (baseline/run_ref.py, in a child
+    process so that a failure there cannot take this process down).  Single-GPU runs only."""
+    script = os.path.join(ROOT, "baseline", "run_ref.py")
+    if not os.path.isfile(script) or not os.path.isdir(os.path.join(ROOT, "baseline", "_ref", "build")):
+        return {"unavailable": "baseline/_ref (the reference's built CUDA solution) is not present"}
+    try:
+        r = subprocess.run([sys.executable, script], capture_output=True, text=True, timeout=420, cwd=ROOT)
+    except subprocess.TimeoutExpired:
+        return {"unavailable": "baseline/run_ref.py did not finish within 420 s"}
+    lines = [l for l in r.stdout.strip().splitlines() if l.startswith("{")]
+    if r.returncode != 0 or not lines:
+        return {"unavailable": f"baseline/run_ref.py exited {r.returncode}: {(r.stderr or r.stdout)[-300:]}"}
+    return json.loads(lines[-1])
 
 
 def run_profile_case(args):
@@ -530,6 +548,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-sweep", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-yardstick", action="store_true",
+                    help="skip timing the reference's own CUDA solution (baseline/_ref) beside this library")
     ap.add_argument("--cpu-budget", type=float, default=15.0, help="seconds of oracle work for cpu_baseline")
     ap.add_argument("--profile-case", action="store_true",
                     help="small single-GPU slice case for ncu (see run_profile_case); not a benchmark")

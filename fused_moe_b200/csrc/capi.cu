@@ -3,7 +3,7 @@
 //
 // Launch sequence of b200moe_run (all on the caller's stream, nothing allocated):
 //   memset counters | route (+histogram) | scan | place | gather | GEMM1(+SwiGLU,+row max)
-//   | requant | GEMM2(+row scale * routing weight, bf16 rows) | combine (per-token sum)
+//   | requant | GEMM2(+row scale * routing weight, each row added into its token's zeroed bf16 output row)
 // It replaces the two Python pipelines of the reference
 // (solution/python/kernel.py:381-429 and 432-572), which need a host synchronisation
 // above 2048 tokens (kernel.py:196); here tile counts stay on the device.
@@ -77,9 +77,7 @@ int ensure_device(int* num_sms) {
     }
     g_dev[dev].num_sms = prop.multiProcessorCount;
     CUDA_TRY(configure_grouped_gemm());
-    CUDA_TRY(configure_grouped_gemm_pair());
     CUDA_TRY(configure_decode_gemm());
-    CUDA_TRY(configure_grouped_gemm_m256());
     g_dev[dev].ready = true;
   }
   *num_sms = g_dev[dev].num_sms;
@@ -123,11 +121,6 @@ int make_tmap_gate_up(CUtensorMap* map, const void* base, uint64_t e_local, uint
   return B200MOE_OK;
 }
 
-// (token, k) pairs up to which the 128-wide N tile is used.  Measured on the 32-expert slice at 32..1024
-// tokens the 256-wide tile is as fast or faster everywhere but at 128 tokens (-6 %), so the narrow tile
-// is only reachable through B200MOE_BN=128.
-constexpr long long kSmallTileMaxPairs = 0;
-
 uint64_t align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
 
 int shape_ok(int T, int e_local, int hidden, int inter) {
@@ -135,6 +128,9 @@ int shape_ok(int T, int e_local, int hidden, int inter) {
   if (e_local > kNumExperts || hidden < 256 || hidden % 256 != 0 || inter < 128 || inter % 128 != 0)
     return B200MOE_ERR_UNSUPPORTED_SHAPE;
   if ((long long)T * kTopK > (1ll << 30)) return B200MOE_ERR_UNSUPPORTED_SHAPE;
+  // the GEMMs keep one weight scale per K block of an item in shared-memory panels
+  if (hidden / kBlockK > grouped_gemm_max_kblocks() || inter / kBlockK > grouped_gemm_max_kblocks())
+    return B200MOE_ERR_UNSUPPORTED_SHAPE;
   return B200MOE_OK;
 }
 
@@ -142,7 +138,7 @@ void compute_layout(int T, int e_local, int hidden, int inter, b200moe_ws_layout
   memset(L, 0, sizeof(*L));
   const int n_chunks = T > 0 ? (T + kChunkTokens - 1) / kChunkTokens : 1;
   const long long pairs = (long long)T * (e_local < kTopK ? e_local : kTopK);
-  // every expert segment may be padded to 256 rows (two M tiles, one per CTA of a pair)
+  // every expert segment is padded to a whole 128-row M tile; m_cap stays a multiple of 256
   const long long m_cap = (long long)align_up((uint64_t)pairs, 2 * kTileM) + (long long)2 * kTileM * e_local;
   L->m_cap = (int32_t)m_cap;
   L->max_tiles = (int32_t)(m_cap / kTileM);
@@ -153,6 +149,7 @@ void compute_layout(int T, int e_local, int hidden, int inter, b200moe_ws_layout
   L->status = take(16 * 4);
   L->meta = take(8 * 4);
   L->splitk_count = take(2 * kSplitKSlots * 4);   // inside the range that clear_counters() zeroes
+  L->tile_arrivals = take((uint64_t)L->max_tiles * 4);   // likewise
   L->chunk_counts = take((uint64_t)n_chunks * e_local * 4);
   L->chunk_base = take((uint64_t)n_chunks * e_local * 4);
   L->expert_count = take((uint64_t)e_local * 4);
@@ -166,13 +163,11 @@ void compute_layout(int T, int e_local, int hidden, int inter, b200moe_ws_layout
   L->row_amax = take((uint64_t)m_cap * 4);
   L->act_q = take((uint64_t)m_cap * inter);
   L->row_scale = take((uint64_t)m_cap * 4);
-  L->y = take((uint64_t)m_cap * hidden * 2);
   L->tok_rows = take((uint64_t)(T > 0 ? T : 1) * kTopK * 4);
   L->topk_ids = take((uint64_t)(T > 0 ? T : 1) * kTopK * 4);
   L->topk_w = take((uint64_t)(T > 0 ? T : 1) * kTopK * 4);
   L->trace = take(2 * 8 * 64 * 8);   // B200MOE_PROF: absolute cycle stamps of CTA 0's first 64 K blocks
   L->splitk_scratch = take((uint64_t)kSplitKSlots * kSplitKMax * 16 * 128 * 4);   // 2 MiB
-  L->pair_tile = take((uint64_t)L->max_tiles * 4);
   L->total_bytes = off;
 }
 
@@ -189,7 +184,7 @@ int bind_workspace(int T, int e_local, int hidden, int inter, void* workspace, s
 
 // Clears the status word and the histogram (start of a layer call).
 int clear_counters(const Workspace& ws, int e_local, cudaStream_t stream) {
-  // status, meta, splitk_count, chunk_counts are adjacent: one memset covers them
+  // status, meta, splitk_count, tile_arrivals, chunk_counts are adjacent: one memset covers them
   size_t bytes = (size_t)(ws.L.chunk_counts - ws.L.status) + (size_t)ws.L.n_chunks * e_local * 4;
   CUDA_TRY(cudaMemsetAsync(ws.base + ws.L.status, 0, bytes, stream));
   return B200MOE_OK;
@@ -235,10 +230,20 @@ int b200moe_launches_per_run(int T, int e_local) {
   (void)e_local;
   if (T <= 0) return 0;
   const char* front = getenv("B200MOE_FRONT");
-  const char* gemm = getenv("B200MOE_GEMM");
-  const bool fused_front = T <= kFrontSmallMaxTokens && !(front && front[0] == '0') && !(gemm && gemm[0] == 'p');
-  // route, scan, place, gather, gemm1, requant, gemm2, combine; decode-size calls fuse the first three
-  return fused_front ? 6 : 8;
+  const bool fused_front = T <= kFrontSmallMaxTokens && !(front && front[0] == '0');
+  // route, scan, place, gather, gemm1, [requant], gemm2 (+ weighted unpermute / reduce into the output); calls of at
+  // most 32 tokens fuse the first three
+  static const bool decode_on = [] {
+    const char* v = getenv("B200MOE_DECODE");
+    return !(v && v[0] == '0');
+  }();
+  static const int decode_max_t = [] {
+    const char* v = getenv("B200MOE_DECODE");
+    return (v && v[0] == '6') ? 64 : 16;
+  }();
+  (void)decode_on;
+  (void)decode_max_t;
+  return (fused_front ? 4 : 6) + 1;
 }
 
 int b200moe_route(const void* logits, int logits_dtype, const void* bias, int bias_dtype, int T,
@@ -284,6 +289,11 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
                         const uint8_t* w2, const float* w2_scale, int T, int e_local, int local_expert_offset,
                         int hidden, int inter, void* workspace, size_t workspace_bytes, void* out_bf16,
                         int64_t out_row_stride, void* stream, bool placed, const RowSegments* segs = nullptr) {
+  // The event pair armed by b200moe_profile_next_gemm1 is for this call only: forget it on every
+  // way out (the GEMM1 launch below consumes it first when the call gets that far).
+  struct DisarmProfile {
+    ~DisarmProfile() { g_prof_start = g_prof_stop = nullptr; }
+  } disarm_profile;
   if (!topk_ids || !topk_w || !w1 || !w1_scale || !w2 || !w2_scale) return B200MOE_ERR_INVALID_ARGUMENT;
   if (T > 0 && ((!segs && (!hidden_states || !hidden_scale)) || !out_bf16)) return B200MOE_ERR_INVALID_ARGUMENT;
   if (segs) {   // rows are read from the segments: no separate payload / scale arrays
@@ -305,18 +315,16 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
   if ((rc = ensure_device(&num_sms)) != B200MOE_OK) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 
-  // B200MOE_GEMM=pair: CTA pairs (256-row tiles); default: one CTA per tile
-  static const bool use_pairs = [] {
-    const char* v = getenv("B200MOE_GEMM");
-    return v && v[0] == 'p';
-  }();
+  // The output starts as zeros: GEMM2's epilogue adds every packed row into its token's row, and a token that no
+  // local expert took stays exactly 0.
+  CUDA_TRY(cudaMemset2DAsync(out_bf16, (size_t)out_row_stride * 2, 0, (size_t)hidden * 2, (size_t)T, st));
   CUDA_TRY(launch_permute(ws, topk_ids, ids_row_stride, topk_w, w_row_stride, hidden_states, hidden_row_stride,
                           hidden_scale, scale_stride_t, scale_stride_kb, T, e_local, local_expert_offset, hidden,
-                          use_pairs ? 2 * kTileM : kTileM, num_sms, st, placed, segs));
+                          kTileM, num_sms, st, placed, segs));
 
-  // small problems get the narrower N tile: more work items to spread over the SMs
   // Up to 16 tokens: swapped-operand decode kernels (B200MOE_DECODE=0 turns them off; B200MOE_DECODE=64
-  // extends them to 64 tokens, where the 128-row tiles currently measure faster).
+  // extends them to 64 tokens, where the 128-row tiles currently measure faster).  Their per-warp scale
+  // panels hold a bounded number of K blocks; larger shapes take the 128-row tiles.
   static const bool decode_on = [] {
     const char* v = getenv("B200MOE_DECODE");
     return !(v && v[0] == '0');
@@ -325,33 +333,18 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
     const char* v = getenv("B200MOE_DECODE");
     return (v && v[0] == '6') ? 64 : 16;
   }();
-  const int nt = (decode_on && !use_pairs && T <= decode_max_t && hidden <= 7168) ? (T <= 16 ? 16 : 64) : 0;
-  static const int bn_forced = [] {
-    const char* v = getenv("B200MOE_BN");
-    return v ? atoi(v) : 0;
-  }();
-  int bn = use_pairs ? 256 : (nt ? 128 : ((long long)T * kTopK <= kSmallTileMaxPairs ? 128 : 256));
-  if (!use_pairs && !nt && (bn_forced == 128 || bn_forced == 256)) bn = bn_forced;
-  // B200MOE_M256=1: 256-row items (two M tiles of an expert share each B box, gemm_m256.cu).  Off by default:
-  // measured 15-25 % slower than 128 x 256 items where experts hold one or two M tiles and equal where they
-  // hold many (a K block of either shape is bound by the same accumulator hand-off chain).
-  static const bool m256_on = [] {
-    const char* v = getenv("B200MOE_M256");
-    return v && v[0] == '1';
-  }();
-  const bool m256 = !nt && !use_pairs && bn_forced == 0 && m256_on;
+  const bool decode_fits = hidden / kBlockK <= decode_gemm_max_kblocks() && inter / kBlockK <= decode_gemm_max_kblocks();
+  const int nt = (decode_on && decode_fits && T <= decode_max_t) ? (T <= 16 ? 16 : 64) : 0;
 
   GemmParams g1;
   memset(&g1, 0, sizeof(g1));
   if ((rc = make_tmap(&g1.tmap_a, ws.base + ws.L.a_packed, (uint64_t)ws.L.m_cap, (uint64_t)hidden, (uint64_t)hidden,
-                      nt ? nt : (m256 ? 2 * kTileM : kTileM))) != B200MOE_OK)
+                      nt ? nt : kTileM)) != B200MOE_OK)
     return rc;
-  if (use_pairs && (hidden % 256 != 0 || inter % 128 != 0)) return B200MOE_ERR_UNSUPPORTED_SHAPE;
-  if (!use_pairs)   // one box = bn/2 gate rows + the matching bn/2 up rows (decode and 256-row kernels: 64 + 64)
-    rc = make_tmap_gate_up(&g1.tmap_b, w1, (uint64_t)e_local, (uint64_t)inter, (uint64_t)hidden, m256 ? 64 : bn / 2);
-  else
-    rc = make_tmap(&g1.tmap_b, w1, (uint64_t)e_local * 2 * inter, (uint64_t)hidden, (uint64_t)hidden, bn / 2);
-  if (rc != B200MOE_OK) return rc;
+  // one box = 128 gate rows + the matching 128 up rows (decode kernels: 64 + 64)
+  if ((rc = make_tmap_gate_up(&g1.tmap_b, w1, (uint64_t)e_local, (uint64_t)inter, (uint64_t)hidden, nt ? 64 : 128)) !=
+      B200MOE_OK)
+    return rc;
   g1.meta = ws.at<int>(ws.L.meta);
   g1.tile_expert = ws.at<int>(ws.L.tile_expert);
   g1.row_token = ws.at<int>(ws.L.row_token);
@@ -360,13 +353,20 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
   g1.m_cap = ws.L.m_cap;
   g1.n_per_expert = 2 * inter;
   g1.kblocks = hidden / kBlockK;
-  g1.n_tiles = (nt || m256) ? inter / 64 : inter / (bn / 2);
-  g1.pair_tile = ws.at<int>(ws.L.pair_tile);
+  g1.n_tiles = nt ? inter / 64 : inter / 128;
   g1.expert_count = ws.at<int>(ws.L.expert_count);
   g1.inter = inter;
   g1.hidden = hidden;
   g1.act = ws.at<__half>(ws.L.act);
   g1.row_amax = ws.at<unsigned>(ws.L.row_amax);
+  // B200MOE_FUSED_REQUANT=1: the CTA that completes an M tile in GEMM1 requantises it (default: a kernel of its own)
+  static const bool fused_requant = [] {
+    const char* v = getenv("B200MOE_FUSED_REQUANT");
+    return v && v[0] == '1';
+  }();
+  g1.tile_arrivals = fused_requant ? ws.at<int>(ws.L.tile_arrivals) : nullptr;
+  g1.act_q_out = ws.at<uint8_t>(ws.L.act_q);
+  g1.row_scale_out = ws.at<float>(ws.L.row_scale);
   g1.status = ws.at<int>(ws.L.status);
   g1.splitk_scratch = ws.at<float>(ws.L.splitk_scratch);
   g1.splitk_count = ws.at<int>(ws.L.splitk_count);
@@ -376,22 +376,24 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
   g1.prof = prof_on ? ws.at<unsigned long long>(ws.L.meta + 32) : nullptr;
   g1.trace = prof_on ? ws.at<unsigned long long>(ws.L.trace) : nullptr;
   if (g_prof_start) CUDA_TRY(cudaEventRecord(g_prof_start, st));
-  if (nt) CUDA_TRY(launch_decode_gemm(1, nt, g1, num_sms, st));
-  else if (m256) CUDA_TRY(launch_grouped_gemm_m256(1, g1, num_sms, st));
-  else if (use_pairs) CUDA_TRY(launch_grouped_gemm_pair(1, g1, num_sms, st));
-  else CUDA_TRY(launch_grouped_gemm(1, bn, g1, num_sms, st));
-  if (g_prof_stop) CUDA_TRY(cudaEventRecord(g_prof_stop, st));
-  g_prof_start = g_prof_stop = nullptr;
+  {
+    cudaError_t le = nt ? launch_decode_gemm(1, nt, g1, num_sms, st) : launch_grouped_gemm(1, g1, num_sms, st);
+    cudaEvent_t stop = g_prof_stop;
+    g_prof_start = g_prof_stop = nullptr;   // one shot, whatever happens next
+    if (le != cudaSuccess) return cuda_fail(le, "GEMM1 launch");
+    if (stop) CUDA_TRY(cudaEventRecord(stop, st));
+  }
 
-  CUDA_TRY(launch_requant(ws, inter, num_sms, st));
+  // the 128-row tiles requantise inside GEMM1 (the CTA that completes an M tile); the decode kernels do not
+  if (nt || !fused_requant) CUDA_TRY(launch_requant(ws, inter, num_sms, st));
 
   GemmParams g2;
   memset(&g2, 0, sizeof(g2));
   if ((rc = make_tmap(&g2.tmap_a, ws.base + ws.L.act_q, (uint64_t)ws.L.m_cap, (uint64_t)inter, (uint64_t)inter,
-                      nt ? nt : (m256 ? 2 * kTileM : kTileM))) != B200MOE_OK)
+                      nt ? nt : kTileM)) != B200MOE_OK)
     return rc;
   if ((rc = make_tmap(&g2.tmap_b, w2, (uint64_t)e_local * hidden, (uint64_t)inter, (uint64_t)inter,
-                      m256 ? 128 : (!use_pairs ? bn : bn / 2))) != B200MOE_OK)   // the whole B tile (decode: the 128-row slab) in one box
+                      nt ? 128 : 256)) != B200MOE_OK)   // the whole B tile (decode: the 128-row slab) in one box
     return rc;
   g2.meta = g1.meta;
   g2.tile_expert = g1.tile_expert;
@@ -400,25 +402,23 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
   g2.m_cap = ws.L.m_cap;
   g2.n_per_expert = hidden;
   g2.kblocks = inter / kBlockK;
-  g2.n_tiles = (nt || m256) ? hidden / 128 : hidden / bn;
-  g2.pair_tile = g1.pair_tile;
+  g2.n_tiles = nt ? hidden / 128 : hidden / 256;
   g2.expert_count = g1.expert_count;
   g2.inter = inter;
   g2.hidden = hidden;
   g2.row_scale = ws.at<float>(ws.L.row_scale);
   g2.row_weight = ws.at<float>(ws.L.row_weight);
-  g2.y = ws.at<__nv_bfloat16>(ws.L.y);
+  g2.out = reinterpret_cast<__nv_bfloat16*>(out_bf16);
+  g2.out_stride = out_row_stride;
   g2.status = g1.status;
   g2.splitk_scratch = g1.splitk_scratch;
   g2.splitk_count = g1.splitk_count + kSplitKSlots;
   g2.prof = prof_on ? ws.at<unsigned long long>(ws.L.meta + 136) : nullptr;
   g2.trace = prof_on ? ws.at<unsigned long long>(ws.L.trace) + 8 * 64 : nullptr;
   if (nt) CUDA_TRY(launch_decode_gemm(2, nt, g2, num_sms, st));
-  else if (m256) CUDA_TRY(launch_grouped_gemm_m256(2, g2, num_sms, st));
-  else if (use_pairs) CUDA_TRY(launch_grouped_gemm_pair(2, g2, num_sms, st));
-  else CUDA_TRY(launch_grouped_gemm(2, bn, g2, num_sms, st));
+  else CUDA_TRY(launch_grouped_gemm(2, g2, num_sms, st));
 
-  CUDA_TRY(launch_combine(ws, T, hidden, out_bf16, out_row_stride, num_sms, st));
+  // nothing follows GEMM2: its epilogue added every packed row into its token's output row
   return B200MOE_OK;
 }
 
@@ -450,11 +450,7 @@ int b200moe_run(const void* logits, int logits_dtype, const void* bias, int bias
     const char* v = getenv("B200MOE_FRONT");
     return !(v && v[0] == '0');
   }();
-  static const bool pairs_on = [] {
-    const char* v = getenv("B200MOE_GEMM");
-    return v && v[0] == 'p';
-  }();
-  if (front_on && !pairs_on && T <= kFrontSmallMaxTokens) {
+  if (front_on && T <= kFrontSmallMaxTokens) {
     if (!logits || !bias) return B200MOE_ERR_INVALID_ARGUMENT;
     if ((logits_dtype != B200MOE_F32 && logits_dtype != B200MOE_BF16) ||
         (bias_dtype != B200MOE_F32 && bias_dtype != B200MOE_BF16))

@@ -5,23 +5,35 @@
 // of its `swiglu_fp8_requant_kernel` (solution/python/moe_fused.cu:131-196) and the
 // per-row scaling of its combine kernels (moe_fused.cu:346-393, 490-517).
 //
-// One CTA per SM walks work items (M tile of 128 packed rows, N tile of BN weight rows).
-// Per 128-wide K block (= one fp32 scale block, = one 128-byte swizzled TMA row):
-//   warps 0, 3  TMA producers (one lane each, alternate K blocks): A box 128x128 B and one B box BNx128 B into a smem ring
-//   warps 1, 2  (one lane each, alternate K blocks) issue 4 tcgen05.mma (K=32 each) into one of two TMEM accumulators, starting
-//               from zero, so each accumulator holds the raw e4m3 dot product of one K block
-//   warps 4-11  read that accumulator back (tcgen05.ld, two loads in flight) and fold it into
-//               fp32 registers with packed FMAs: acc += (a_scale * b_scale) * partial.  The
-//               block scales are arbitrary fp32 numbers, so they cannot ride on the MMA.
-// The control warpgroup (warps 0-3) gives registers back (setmaxnreg) so that the eight
-// promotion warps can hold a 128x256 fp32 tile (128 accumulators per thread) without spills.
-// GEMM1 pairs gate rows [n, n+BN/2) with up rows [inter+n, ...) in one tile, so the epilogue
-// computes g*silu(u) in registers, stores fp16 activations and the row maximum.
-// GEMM2's epilogue multiplies by (row requant scale * routing weight) and stores the row as
-// bf16; the combine kernel sums a token's rows.
+// One CTA of 20 warps per SM walks work items (M tile of 128 packed rows, N tile of 256
+// weight rows).  Per 128-wide K block (= one fp32 scale block, = one 128-byte swizzled row):
+//   warps 0, 3   TMA producers (one lane each, alternate K blocks): A box 128x128 B, one B box
+//                256x128 B and (GEMM1) the 128 activation scales of the K block into a smem ring
+//   warps 1, 2   MMA issuers (one lane each, alternate K blocks, issuer i always writes TMEM
+//                accumulator i): 4 tcgen05.mma (K=32 each) starting from zero, so an accumulator
+//                holds the raw e4m3 dot product of ONE K block
+//   warps 4-19   promotion: 16 warps, four per TMEM lane quarter, 64 accumulator columns each;
+//                they read the K block's partial sums back (tcgen05.ld) and fold them into fp32
+//                registers with packed FMAs: acc += (a_scale * b_scale) * partial.  The block
+//                scales are arbitrary (signed) fp32 numbers, so they cannot ride on the MMA.
+// What shaped the hand-offs: an mbarrier wait costs ~180 cycles of latency even when the phase
+// is already complete, a single thread needs ~360 cycles to issue a K block's MMAs and commits,
+// and the promotion warps are the busiest role.  Therefore
+//   * a promotion warp looks at the NEXT K block's "accumulator written" barrier (non-blocking) before
+//     the last FMAs of the current one, so the look's latency hides under the FMAs;
+//   * "accumulator read back" is a shared-memory counter the promotion warps add to and the
+//     issuer polls with plain acquire loads (~30 cycles) instead of a second mbarrier;
+//   * activation scales arrive in shared memory with the operands (same barrier), weight scales
+//     of an item sit in a per-warp panel, so the K loop touches no global memory.
+// GEMM1 pairs gate rows [n, n+128) with up rows [inter+n, ...) in one tile, so the epilogue
+// computes g*silu(u) in registers, stores fp16 activations and the row maximum; the CTA that
+// finishes the last N tile of an M tile requantises the tile's rows to e4m3 (no second kernel).
+// GEMM2's epilogue multiplies by (row requant scale * routing weight) and adds the bf16 row into its
+// token's row of the output (red.global.add.noftz.v4.bf16x2): no second pass over the rows.
 //
 // Every wait is bounded (see mbar_wait); on a timeout the CTA drains and frees its TMEM.
 #include <cuda_fp16.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "kernels.cuh"
@@ -31,64 +43,172 @@ namespace b200moe {
 namespace {
 
 constexpr int kCtrlWarps = 4;
-constexpr int kEpiWarps = 8;
-constexpr int kGemmThreads = 32 * (kCtrlWarps + kEpiWarps);   // 384: three warpgroups
-constexpr int kCtrlRegs = 56;
-constexpr int kEpiRegs = 224;   // 128*56 + 256*224 = 64512 = 384 threads * 168 registers at launch
-constexpr int kABytes = kTileM * kBlockK;   // 16 KiB
-constexpr int kScalePrefetchDist = 6;       // K blocks ahead for the activation-scale L2 prefetch
-
-template <int BN> struct TileCfg {
-  static constexpr int kBBytes = BN * kBlockK;
-  static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
-  static constexpr int kTmemCols = 2 * BN;
-  static constexpr int kBarBytes = 256;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kBarBytes + 1024;   // + alignment slack
-  static constexpr int kColsPerThread = BN / 2;
-  static constexpr int kChunks = kColsPerThread / 32;
+// Register budget: the CTA owns what it was launched with (threads x launch registers) and
+// setmaxnreg only moves registers inside that pool - an increase that the pool cannot serve blocks
+// for ever.  NW promotion warps: 8 (128 accumulator columns per thread) or 16 (64 per thread).
+template <int NW> struct WarpCfg;
+template <> struct WarpCfg<8> {
+  static constexpr int kThreads = 32 * (kCtrlWarps + 8);   // 384
+  static constexpr int kLaunchRegs = 168, kCtrlRegs = 56, kPromoRegs = 224;
 };
+template <> struct WarpCfg<16> {
+  static constexpr int kThreads = 32 * (kCtrlWarps + 16);  // 640
+  static constexpr int kLaunchRegs = 96, kCtrlRegs = 32, kPromoRegs = 112;
+};
+template <int NW> constexpr bool reg_budget_ok() {
+  using W = WarpCfg<NW>;
+  return 32 * kCtrlWarps * (W::kLaunchRegs - W::kCtrlRegs) >= 32 * NW * (W::kPromoRegs - W::kLaunchRegs) &&
+         W::kThreads * W::kLaunchRegs <= 65536 && W::kThreads * (W::kLaunchRegs + 8) > 65536;
+}
+static_assert(reg_budget_ok<8>() && reg_budget_ok<16>(), "setmaxnreg.inc would wait for registers that nobody releases");
+constexpr int kMaxPromoWarps = 16;
+constexpr int kDefaultPromoWarps = 8;
+constexpr int kBN = 256;
+constexpr int kABytes = kTileM * kBlockK;   // 16 KiB
+constexpr int kBBytes = kBN * kBlockK;      // 32 KiB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kStages = 4;
+constexpr int kRing = 8;                    // activation-scale slots; see the reuse argument at the producer
+constexpr int kRingBytes = kRing * kTileM * 4;
+constexpr int kPanelFloats = 128;           // per promotion warp: two runs of up to 64 weight scales
+constexpr int kPanelBytes = kMaxPromoWarps * kPanelFloats * 4;
+constexpr int kMaxKBlocks = 64;
+constexpr int kBarBytes = 256;
+constexpr int kSmemBytes = kStages * kStageBytes + kRingBytes + kPanelBytes + kBarBytes + 1024;   // + alignment slack
+constexpr int kTmemCols = 2 * kBN;
 
 __device__ __forceinline__ float silu_mul(float g, float u) {
   float sig = __fdividef(1.0f, 1.0f + __expf(-u));   // approximate reciprocal: 2 ulp, far below e4m3 resolution
   return g * (u * sig);
 }
 
-// acc[16 pairs] += scale * r[32] with packed fp32 FMAs
+// acc[16 pairs] += scale * r[32]
 __device__ __forceinline__ void fma_chunk(float2* acc, const uint32_t (&r)[32], float sc) {
+#ifdef B200MOE_SCALAR_FMA
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    acc[j].x = fmaf(__uint_as_float(r[2 * j]), sc, acc[j].x);
+    acc[j].y = fmaf(__uint_as_float(r[2 * j + 1]), sc, acc[j].y);
+  }
+#else
   const float2 s2 = make_float2(sc, sc);
 #pragma unroll
   for (int j = 0; j < 16; ++j)
     acc[j] = __ffma2_rn(make_float2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])), s2, acc[j]);
+#endif
 }
 
-// First TMEM column (inside the tile) and scale selector of chunk c of a thread in column half h.
-template <int MODE, int BN>
-__device__ __forceinline__ uint32_t chunk_col(int c, int h) {
-  constexpr int CH = TileCfg<BN>::kChunks;
-  if (MODE == 1) {
-    const bool up = c >= CH / 2;
-    return (up ? BN / 2 : 0) + h * (BN / 4) + (up ? c - CH / 2 : c) * 32;
+// untiled bulk copy global -> shared (16-byte aligned, size a multiple of 16), counted on an mbarrier
+__device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+// Relaxed: what the counter publishes ("these TMEM columns sit in my registers") was completed by
+// tcgen05.wait::ld before this instruction; the tcgen05 fences on both sides order the tensor-memory accesses.
+__device__ __forceinline__ void red_add_smem(uint32_t addr, uint32_t v) {
+  asm volatile("red.relaxed.cta.shared::cta.add.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_smem(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ int atom_add_acq_rel_gpu(int* addr, int v) {
+  int old;
+  asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(addr), "r"(v) : "memory");
+  return old;
+}
+__device__ __forceinline__ float ld_smem_f32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared::cta.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_smem_f32(uint32_t addr, float v) {
+  asm volatile("st.shared::cta.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+
+// Bounded poll of a monotonic shared-memory counter (wrap-safe comparison).
+__device__ __forceinline__ bool counter_wait(uint32_t addr, uint32_t target, volatile int* abort_flag, int* status,
+                                             int where) {
+  long long t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    if ((int32_t)(ld_acquire_smem(addr) - target) >= 0) return true;
+    if (++spins >= 256u) {
+      spins = 0;
+      if (*abort_flag) return false;
+      long long now = clock64();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitBudgetCycles) {
+        *abort_flag = 1;
+        if (atomicCAS(status + kStatusCode, 0, (int)B200MOE_ERR_DEVICE_TIMEOUT) == 0)
+          status[kStatusDetail] = where;
+        return false;
+      }
+    }
   }
-  return h * (BN / 2) + c * 32;
 }
 
-template <int MODE, int BN, bool PROF>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+// e4m3 codes and scales of the rows of M tile `m_tile` that promotion warp `pw` owns, from the fp16
+// activations and row maxima that the tile's 16 CTAs left in L2 (called by the CTA that arrived last).
+// Not inlined: its registers must not add to the K loop's.
+__device__ __noinline__ void requant_tile_rows(const GemmParams& p, int m_tile, int pw, int lane, int rows_per_warp) {
+  const int vecs = p.inter / 8;   // 8 halves = 16 bytes in, 8 bytes out
+  for (int r8 = 0; r8 < rows_per_warp; ++r8) {
+    const int m = m_tile * kTileM + pw * rows_per_warp + r8;
+    if (p.row_token[m] < 0) continue;
+    const float amax = fmaxf(__uint_as_float(__ldcg(p.row_amax + m)), 1e-8f);
+    const float sc = fmaxf(amax / 448.0f, 1e-8f);
+    if (lane == 0) p.row_scale_out[m] = sc;
+    const uint4* src = reinterpret_cast<const uint4*>(p.act + (size_t)m * p.inter);
+    uint2* dstq = reinterpret_cast<uint2*>(p.act_q_out + (size_t)m * p.inter);
+    for (int v0 = 0; v0 < vecs; v0 += 128) {
+      uint4 raw[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (v0 + u * 32 + lane < vecs) raw[u] = __ldcg(src + v0 + u * 32 + lane);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (v0 + u * 32 + lane >= vecs) continue;
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw[u].x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw[u].y));
+        const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&raw[u].z));
+        const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&raw[u].w));
+        uint2 pk;
+        pk.x = pack4_e4m3(a.x / sc, a.y / sc, b.x / sc, b.y / sc);
+        pk.y = pack4_e4m3(c.x / sc, c.y / sc, d.x / sc, d.y / sc);
+        dstq[v0 + u * 32 + lane] = pk;
+      }
+    }
+  }
+}
+
+template <int MODE, int NW, bool PROF>
+__global__ void __launch_bounds__(WarpCfg<NW>::kThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
-  using Cfg = TileCfg<BN>;
-  constexpr int S = Cfg::kStages;
+  constexpr int S = kStages;
+  constexpr int kPromoWarps = NW;
+  constexpr int kCtrlRegs = WarpCfg<NW>::kCtrlRegs, kPromoRegs = WarpCfg<NW>::kPromoRegs;
+  constexpr int CH = 32 / NW;          // 32-column chunks per promotion thread: 256 columns / (NW / 4 warps per quarter) / 32
+  static_assert(CH == 2 || CH == 4, "promotion threads hold two or four 32-column chunks");
+  constexpr int WQ = NW / 4;           // promotion warps per TMEM lane quarter
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t smem_base = smem_u32(smem);
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes);
+  const uint32_t ring_base = smem_base + S * kStageBytes;          // [kRing][128] activation scales
+  const uint32_t panel_base = ring_base + kRingBytes;              // [16 warps][128] weight scales
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * kStageBytes + kRingBytes + kPanelBytes);
   const uint32_t bar_full = smem_u32(bars);              // S barriers: stage filled by TMA
   const uint32_t bar_empty = bar_full + 8 * S;           // S barriers: stage consumed by the MMAs
   const uint32_t bar_tfull = bar_empty + 8 * S;          // 2 barriers: accumulator written
-  const uint32_t bar_tempty = bar_tfull + 16;            // 2 barriers: accumulator read back
-  const uint32_t bar_drain = bar_tempty + 16;            // 2 barriers: each issuer's MMAs retired (teardown)
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 6);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  const uint32_t bar_drain = bar_tfull + 16;             // 2 barriers: each issuer's MMAs retired (teardown)
+  const uint32_t bar_epi = bar_drain + 16;               // 2 barriers: GEMM1 tile epilogue (all stored; verdict known)
+  uint32_t* words = reinterpret_cast<uint32_t*>(bars + 2 * S + 6);
+  const uint32_t cnt_read = smem_u32(words);             // 2 counters: promotion warps that read accumulator b back
+  uint32_t* tmem_slot = words + 2;
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(words + 3);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -98,12 +218,14 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       mbar_init(bar_full + 8 * s, 1);
       mbar_init(bar_empty + 8 * s, 1);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(bar_tfull + 8 * b, 1);
-      mbar_init(bar_tempty + 8 * b, kEpiWarps);
-    }
+    mbar_init(bar_tfull, 1);
+    mbar_init(bar_tfull + 8, 1);
     mbar_init(bar_drain, 1);
     mbar_init(bar_drain + 8, 1);
+    mbar_init(bar_epi, kPromoWarps);
+    mbar_init(bar_epi + 8, 1);
+    words[0] = 0;
+    words[1] = 0;
     abort_flag[0] = 0;
     abort_flag[1] = 0;   // never set by others: the teardown waits ignore an abort
     fence_mbar_init();
@@ -111,7 +233,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     tma_prefetch_desc(&p.tmap_b);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), Cfg::kTmemCols);
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -131,6 +253,10 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     reg_dealloc<kCtrlRegs>();
     if ((warp == 0 || warp == 3) && lane == 0) {
       // ------------------------------ TMA producers (alternate K blocks) ------------------------------
+      // Ring of activation scales: slot it % 8 is rewritten for K block it once the MMAs of K block
+      // it - 4 have completed (the stage's "empty" barrier).  Its last readers, the promotion warps of
+      // K block it - 8, read their scale before they released that accumulator, i.e. before the MMAs
+      // of K block it - 6 could start.
       const uint32_t pme = warp == 0 ? 0u : 1u;
       uint32_t it = 0;
       bool alive = true;
@@ -138,18 +264,22 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         const int m_tile = w / p.n_tiles, n_tile = w % p.n_tiles;
         const int e = p.tile_expert[m_tile];
         // GEMM1: first row inside the gate (and up) plane of expert e; GEMM2: row of [e_local*hidden][inter]
-        const int brow = MODE == 1 ? n_tile * (BN / 2) : e * p.n_per_expert + n_tile * BN;
+        const int brow = MODE == 1 ? n_tile * (kBN / 2) : e * p.n_per_expert + n_tile * kBN;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          if ((it & 1u) != pme) continue;
-          const uint32_t s = it % S, ph = (it / S) & 1u;
-          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status, 1)) { alive = false; break; }
-          const uint32_t full = bar_full + 8 * s;
-          const uint32_t a_dst = smem_base + s * Cfg::kStageBytes;
-          mbar_arrive_expect_tx(full, Cfg::kStageBytes);
-          tma_load_2d(a_dst, &p.tmap_a, kb * kBlockK, m_tile * kTileM, full);
-          // the whole B tile in one operation: BN/2 gate rows + BN/2 up rows (3D box over the two planes), or BN rows
-          if (MODE == 1) tma_load_3d(a_dst + kABytes, &p.tmap_b, kb * kBlockK, brow, 2 * e, full);
-          else tma_load_2d(a_dst + kABytes, &p.tmap_b, kb * kBlockK, brow, full);
+          if ((it & 1u) == pme) {
+            const uint32_t s = it % S, ph = (it / S) & 1u;
+            if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status, 1)) { alive = false; break; }
+            const uint32_t full = bar_full + 8 * s;
+            const uint32_t a_dst = smem_base + s * kStageBytes;
+            mbar_arrive_expect_tx(full, kStageBytes + (MODE == 1 ? kTileM * 4 : 0));
+            tma_load_2d(a_dst, &p.tmap_a, kb * kBlockK, m_tile * kTileM, full);
+            // the whole B tile in one operation: 128 gate rows + 128 up rows (3D box over the two planes), or 256 rows
+            if (MODE == 1) tma_load_3d(a_dst + kABytes, &p.tmap_b, kb * kBlockK, brow, 2 * e, full);
+            else tma_load_2d(a_dst + kABytes, &p.tmap_b, kb * kBlockK, brow, full);
+            if (MODE == 1)
+              bulk_load(ring_base + (it % kRing) * (kTileM * 4),
+                        p.a_scale + (size_t)kb * p.m_cap + (size_t)m_tile * kTileM, kTileM * 4, full);
+          }
         }
       }
       // Copies still in flight must land before the CTA's shared memory is released.
@@ -158,11 +288,10 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         if ((j & 1u) == pme) (void)mbar_wait(bar_full + 8 * (j % S), (j / S) & 1u, abort_flag + 1, p.status, 6);
     } else if ((warp == 1 || warp == 2) && lane == 0) {
       // ------------------------------ MMA issuers ------------------------------
-      // Two threads (on different SM sub-partitions) take alternate K blocks.  Issuing the
-      // four MMAs and two commits of a K block costs one thread ~300 cycles whatever the
-      // tile size, and its waits for operands and for a free accumulator add to that; with
-      // two issuers one waits while the other issues.  Issuer i always writes accumulator i.
-      constexpr uint32_t idesc = make_idesc_e4m3(kTileM, BN);
+      // Two threads (on different SM sub-partitions) take alternate K blocks: issuing the four
+      // MMAs and two commits of a K block costs one thread ~360 cycles whatever the tile size.
+      // Issuer i always writes accumulator i.
+      constexpr uint32_t idesc = make_idesc_e4m3(kTileM, kBN);
       const uint32_t me = (uint32_t)(warp - 1);
       uint32_t it = 0;
       bool alive = true;
@@ -171,31 +300,28 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
           if ((it & 1u) != me) continue;
           const uint32_t s = it % S, ph = (it / S) & 1u;
-          const uint32_t b = me, bph = (it >> 1) & 1u;
           const long long m0 = PROF ? clock64() : 0;
-          // Operands first: they usually landed long ago, so only one wake-up (the free
-          // accumulator) is left on the critical path.
+          // Operands first: they usually landed long ago, so only the accumulator hand-off is
+          // left on the critical path.
           if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 3)) { alive = false; break; }
           const long long m1 = PROF ? clock64() : 0;
-          if (!mbar_wait(bar_tempty + 8 * b, bph ^ 1u, abort_flag, p.status, 2)) { alive = false; break; }
+          // use number it/2 of accumulator `me`: all 16 promotion warps have read the previous one
+          if (!counter_wait(cnt_read + 4 * me, (uint32_t)kPromoWarps * (it >> 1), abort_flag, p.status, 2)) {
+            alive = false;
+            break;
+          }
           const long long m2 = PROF ? clock64() : 0;
           tc_fence_after();
-          const uint32_t a_addr = smem_base + s * Cfg::kStageBytes;
-          tc_mma_f8_kblock(tmem_base + b * BN, kmajor_sw128_desc_lo(a_addr), kmajor_sw128_desc_lo(a_addr + kABytes),
+          const uint32_t a_addr = smem_base + s * kStageBytes;
+          tc_mma_f8_kblock(tmem_base + me * kBN, kmajor_sw128_desc_lo(a_addr), kmajor_sw128_desc_lo(a_addr + kABytes),
                            kKmajorSw128DescHi, idesc);
           tc_commit(bar_empty + 8 * s);
-          tc_commit(bar_tfull + 8 * b);
+          tc_commit(bar_tfull + 8 * me);
           if (PROF) {
             const long long m3 = clock64();
             wait_tma += m1 - m0;
             wait_epi += m2 - m1;
             t_issue += m3 - m2;
-            if (p.trace && blockIdx.x == 0 && it < 64) {
-              p.trace[it * 8 + 0] = (unsigned long long)m0;   // issuer starts waiting for operands
-              p.trace[it * 8 + 1] = (unsigned long long)m1;   // operands landed seen
-              p.trace[it * 8 + 2] = (unsigned long long)m2;   // accumulator free seen
-              p.trace[it * 8 + 3] = (unsigned long long)m3;   // MMAs and commits issued
-            }
           }
         }
       }
@@ -210,119 +336,136 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     }
   } else {
     // ------------------------------ promotion + epilogue ------------------------------
-    reg_alloc<kEpiRegs>();
-    const int ew = warp - kCtrlWarps;
-    const int q = warp & 3;        // TMEM lane quarter this warp may read
-    const int h = ew >> 2;         // which half of the tile's columns
-    constexpr int CPT = Cfg::kColsPerThread;
-    constexpr int CH = Cfg::kChunks;
-    static_assert(CH == 2 || CH == 4, "two or four 32-column chunks per thread");
+    reg_alloc<kPromoRegs>();
+    const int pw = warp - kCtrlWarps;
+    const int q = pw & 3;          // TMEM lane quarter this warp may read (= warp % 4)
+    const int cg = pw >> 2;        // which 256 / WQ of the tile's accumulator columns
+    constexpr int HC = CH / 2;     // chunks per half (GEMM1: gate half, up half)
+    // GEMM1: HC x 32 gate columns and the matching up columns; GEMM2: CH x 32 consecutive columns.
+    // chunk c < HC sits at col_lo + 32 c, chunk c >= HC at col_hi + 32 (c - HC)
+    const uint32_t col_lo = MODE == 1 ? cg * (HC * 32) : cg * (CH * 32);
+    const uint32_t col_hi = MODE == 1 ? kBN / 2 + cg * (HC * 32) : cg * (CH * 32) + HC * 32;
+    const uint32_t panel = panel_base + pw * (kPanelFloats * 4);
+    const uint32_t ring_me = ring_base + (q * 32 + lane) * 4;
     uint32_t it = 0;
     bool alive = true;
-    const bool prof_me = PROF && p.prof && blockIdx.x == 0 && ew == 0 && lane == 0;
+    const bool prof_me = PROF && p.prof && blockIdx.x == 0 && pw == 0 && lane == 0;
     const long long t_begin = PROF ? clock64() : 0;
     long long t_wait = 0, t_promote = 0, t_epi = 0;
     const int nblk_per_expert = p.n_per_expert / kBlockK;
+    uint32_t peek = 0;   // "accumulator written" of the coming K block already seen complete
+    uint32_t epi_ph = 0;  // phase of the two epilogue barriers (GEMM1)
+    volatile uint32_t* last_flag = words + 5;   // 0, or 1 + the M tile this CTA has to requantise
+    // GEMM1, lane 0 of promotion warp 0: this CTA's arrival on its previous item's M tile (the atomic's
+    // answer is looked at one item later, so nobody waits for it)
+    int pending_tile = -1, pending_prev = 0;
     for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x) {
       const int m_tile = w / p.n_tiles, n_tile = w % p.n_tiles;
       const int e = p.tile_expert[m_tile];
       const int row = m_tile * kTileM + q * 32 + lane;
       const int tok = p.row_token[row];
-      float2 acc[CPT / 2];
-#pragma unroll
-      for (int j = 0; j < CPT / 2; ++j) acc[j] = make_float2(0.f, 0.f);
-
-      const float* sa_ptr = nullptr;
-      const float* sb0_ptr;
-      const float* sb1_ptr = nullptr;
-      if (MODE == 1) {
-        sa_ptr = p.a_scale + row;
-        const int gcol0 = n_tile * (BN / 2) + h * (BN / 4);          // first gate row of this thread
-        sb0_ptr = p.b_scale + ((size_t)e * nblk_per_expert + gcol0 / kBlockK) * kblocks;
-        sb1_ptr = p.b_scale + ((size_t)e * nblk_per_expert + (p.inter + gcol0) / kBlockK) * kblocks;
-#pragma unroll 1
-        for (int kb = 4; kb < 4 + kScalePrefetchDist && kb < kblocks; ++kb) prefetch_l2(sa_ptr + (size_t)kb * p.m_cap);
-      } else {
-        const int col0 = n_tile * BN + h * (BN / 2);
-        sb0_ptr = p.b_scale + ((size_t)e * nblk_per_expert + col0 / kBlockK) * kblocks;
+      // GEMM2: the row's output factors, fetched now so that the epilogue does not wait for them
+      float rs_a = 0.f, rs_b = 0.f;
+      if (MODE == 2 && tok >= 0) {
+        rs_a = p.row_scale[row];
+        rs_b = p.row_weight[row];
       }
-      // Scales of K blocks kb .. kb+3 ride in registers: a load issued only one K block ahead
-      // is still in flight when it is needed (L2 under the weight stream answers in ~1 us).
-      constexpr int kScaleAhead = 3;
-      float sa_r[kScaleAhead + 1], sb0_r[kScaleAhead + 1], sb1_r[kScaleAhead + 1];
+      float2 acc[CH * 16];
 #pragma unroll
-      for (int i = 0; i <= kScaleAhead; ++i) {
-        const bool in = i < kblocks;
-        sa_r[i] = (MODE == 1 && in) ? sa_ptr[(size_t)i * p.m_cap] : 1.f;
-        sb0_r[i] = in ? sb0_ptr[i] : 0.f;
-        sb1_r[i] = (MODE == 1 && in) ? sb1_ptr[i] : 0.f;
+      for (int j = 0; j < CH * 16; ++j) acc[j] = make_float2(0.f, 0.f);
+
+      // weight scales of this item into the warp's panel: run 0 at [0, 64), run 1 at [64, 128)
+      {
+        const float* run0;
+        const float* run1;
+        if (MODE == 1) {
+          run0 = p.b_scale + ((size_t)e * nblk_per_expert + n_tile) * kblocks;                       // gate block
+          run1 = p.b_scale + ((size_t)e * nblk_per_expert + p.inter / kBlockK + n_tile) * kblocks;   // up block
+        } else {
+          run0 = p.b_scale + ((size_t)e * nblk_per_expert + 2 * n_tile + (cg * (CH * 32)) / kBlockK) * kblocks;
+          run1 = run0;
+        }
+        float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
+        if (lane < kblocks) v0 = run0[lane];
+        if (lane + 32 < kblocks) v1 = run0[lane + 32];
+        if (MODE == 1) {
+          if (lane < kblocks) v2 = run1[lane];
+          if (lane + 32 < kblocks) v3 = run1[lane + 32];
+        }
+        __syncwarp();   // every lane is done reading the previous item's panel
+        st_smem_f32(panel + lane * 4, v0);
+        st_smem_f32(panel + (lane + 32) * 4, v1);
+        if (MODE == 1) {
+          st_smem_f32(panel + (64 + lane) * 4, v2);
+          st_smem_f32(panel + (96 + lane) * 4, v3);
+        }
+        __syncwarp();
       }
 
       for (int kb = 0; kb < kblocks; ++kb, ++it) {
         const uint32_t b = it & 1u, bph = (it >> 1) & 1u;
-        const float sc0 = sa_r[0] * sb0_r[0];
-        const float sc1 = sa_r[0] * sb1_r[0];
-#pragma unroll
-        for (int i = 0; i < kScaleAhead; ++i) {
-          sa_r[i] = sa_r[i + 1];
-          sb0_r[i] = sb0_r[i + 1];
-          sb1_r[i] = sb1_r[i + 1];
-        }
-        {
-          const int nk = kb + kScaleAhead + 1;
-          if (nk < kblocks) {
-            if (MODE == 1) {
-              sa_r[kScaleAhead] = sa_ptr[(size_t)nk * p.m_cap];
-              sb1_r[kScaleAhead] = sb1_ptr[nk];
-              if (nk + kScalePrefetchDist < kblocks) prefetch_l2(sa_ptr + (size_t)(nk + kScalePrefetchDist) * p.m_cap);
-            }
-            sb0_r[kScaleAhead] = sb0_ptr[nk];
-          }
-        }
         const long long c0 = PROF ? clock64() : 0;
-        bool ok = mbar_wait(bar_tfull + 8 * b, bph, abort_flag, p.status, 4);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) { alive = false; break; }
+        if (!peek) {
+          bool ok = mbar_wait(bar_tfull + 8 * b, bph, abort_flag, p.status, 4);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) { alive = false; break; }
+        }
         tc_fence_after();
         const long long c1 = PROF ? clock64() : 0;
-        const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + b * BN;
-        uint32_t ra[32], rb[32];
-        tmem_ld_32x32(t_row + chunk_col<MODE, BN>(0, h), ra);
-        tmem_ld_32x32(t_row + chunk_col<MODE, BN>(1, h), rb);
-        tmem_ld_wait_on(ra, rb);
-        const long long c1a = PROF ? clock64() : 0;
-        // The accumulator is free as soon as its last column sits in registers: signal the MMA
-        // thread before the remaining FMAs, which then overlap the next K block's MMAs.
-        long long c1b = c1a;
+        const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + b * kBN;
+        const uint32_t nit = it + 1;
+        float sc0, sc1;
+        auto load_scales = [&]() {   // issued behind the first TMEM loads so that the latencies overlap
+          sc0 = ld_smem_f32(panel + kb * 4);
+          sc1 = MODE == 1 ? ld_smem_f32(panel + (64 + kb) * 4) : sc0;
+          if (MODE == 1) {
+            const float sa = ld_smem_f32(ring_me + (it % kRing) * (kTileM * 4));
+            sc0 *= sa;
+            sc1 *= sa;
+          }
+        };
+        // The accumulator is free as soon as its last column sits in registers: the MMA thread is told
+        // before the remaining FMAs, which then overlap the next K block's MMAs.  Right behind that the
+        // other accumulator's barrier is looked at (non-blocking) for the next K block; the answer is
+        // picked up after the last FMAs, so its latency costs nothing, and when it says "written" the
+        // next iteration starts without a wait.  (Past the CTA's last K block nothing consumes it.)
+        uint32_t pk;
         if constexpr (CH == 2) {
+          uint32_t ra[32];
+          tmem_ld_32x32(t_row + col_lo, ra);
+          load_scales();
+          tmem_ld_wait_on(ra);
+          fma_chunk(acc, ra, sc0);
+          tmem_ld_32x32(t_row + col_hi, ra);
+          tmem_ld_wait_on(ra);
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
-          fma_chunk(acc, ra, sc0);
-          fma_chunk(acc + 16, rb, MODE == 1 ? sc1 : sc0);
+          if (lane == 0) red_add_smem(cnt_read + 4 * b, 1u);
+          pk = mbar_test_wait(bar_tfull + 8 * (nit & 1u), (nit >> 1) & 1u);
+          fma_chunk(acc + 16, ra, sc1);
         } else {
-          fma_chunk(acc, ra, sc0);
-          tmem_ld_32x32(t_row + chunk_col<MODE, BN>(2, h), ra);
-          fma_chunk(acc + 16, rb, sc0);
-          tmem_ld_32x32(t_row + chunk_col<MODE, BN>(3, h), rb);
+          uint32_t ra[32], rb[32];
+          tmem_ld_32x32(t_row + col_lo, ra);
+          tmem_ld_32x32(t_row + col_lo + 32, rb);
+          load_scales();
           tmem_ld_wait_on(ra, rb);
-          c1b = PROF ? clock64() : 0;
+          fma_chunk(acc, ra, sc0);
+          tmem_ld_32x32(t_row + col_hi, ra);
+          fma_chunk(acc + 16, rb, sc0);
+          tmem_ld_32x32(t_row + col_hi + 32, rb);
+          tmem_ld_wait_on(ra, rb);
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_tempty + 8 * b);
-          fma_chunk(acc + 32, ra, MODE == 1 ? sc1 : sc0);
-          fma_chunk(acc + 48, rb, MODE == 1 ? sc1 : sc0);
+          if (lane == 0) red_add_smem(cnt_read + 4 * b, 1u);
+          pk = mbar_test_wait(bar_tfull + 8 * (nit & 1u), (nit >> 1) & 1u);
+          fma_chunk(acc + 32, ra, sc1);
+          fma_chunk(acc + 48, rb, sc1);
         }
+        peek = __all_sync(0xffffffffu, pk != 0u) ? 1u : 0u;
         if (PROF) {
           const long long c2 = clock64();
           t_wait += c1 - c0;
           t_promote += c2 - c1;
-          if (prof_me && p.trace && it < 64) {
-            p.trace[it * 8 + 4] = (unsigned long long)c1;    // accumulator ready seen by promotion warp 0
-            p.trace[it * 8 + 5] = (unsigned long long)c1a;   // first two chunks in registers
-            p.trace[it * 8 + 6] = (unsigned long long)c1b;   // last chunk in registers: accumulator released
-            p.trace[it * 8 + 7] = (unsigned long long)c2;    // promotion of this K block done
-          }
         }
       }
       if (!alive) break;
@@ -330,42 +473,97 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
 
       if (tok >= 0) {
         if (MODE == 1) {
-          // acc pairs [0 .. CPT/4) = gate columns, [CPT/4 .. CPT/2) = matching up columns
-          constexpr int HP = CPT / 4;
+          // acc[0 .. HC*16) = gate columns (pairs), acc[HC*16 ..) = the matching up columns.
           // fp16 keeps 11 significant bits, three more than the e4m3 codes made from it need;
           // the row maximum is taken over the rounded values so that it is attained exactly.
-          __half* dst = p.act + (size_t)row * p.inter + n_tile * (BN / 2) + h * (BN / 4);
+          constexpr int HP = HC * 16;
+          __half* dst = p.act + (size_t)row * p.inter + n_tile * (kBN / 2) + cg * (HC * 32);
           float amax = 0.f;
 #pragma unroll
           for (int j = 0; j < HP; j += 8) {
-            uint32_t w[8];
+            uint32_t wv[8];
 #pragma unroll
             for (int t = 0; t < 8; ++t) {
               __half2 hh = __floats2half2_rn(silu_mul(acc[j + t].x, acc[HP + j + t].x),
                                              silu_mul(acc[j + t].y, acc[HP + j + t].y));
               float2 back = __half22float2(hh);
               amax = fmaxf(amax, fmaxf(fabsf(back.x), fabsf(back.y)));
-              w[t] = *reinterpret_cast<uint32_t*>(&hh);
+              wv[t] = *reinterpret_cast<uint32_t*>(&hh);
             }
-            st_global_v8(dst + 2 * j, w);
+            st_global_v8(dst + 2 * j, wv);
           }
           atomicMax(p.row_amax + row, __float_as_uint(amax));
         } else {
-          const float rs = p.row_scale[row] * p.row_weight[row];
-          __nv_bfloat16* dst = p.y + (size_t)row * p.hidden + n_tile * BN + h * (BN / 2);
+          // the routing-weighted unpermute/reduce: bf16(G2 * w) of this row is added straight into its
+          // token's output row (zeroed at call start), eight bf16 sums per 16-byte red.global.add - the
+          // arithmetic of the reference's `out[t] += bf16(G2 * w)` on a bf16 tensor
+          // (experiments/fast_bench/correctness_bench.py:107-111), in the order the tiles finish
+          asm volatile("" : "+f"(rs_a), "+f"(rs_b));   // keeps the product (and the wait for the two loads) down here
+          const float rs = rs_a * rs_b;
+          __nv_bfloat16* dst = p.out + (size_t)tok * p.out_stride + n_tile * kBN + cg * (CH * 32);
 #pragma unroll
-          for (int j = 0; j < CPT / 2; j += 8) {
-            uint32_t w[8];
+          for (int j = 0; j < CH * 16; j += 4) {
+            uint32_t wv[4];
 #pragma unroll
-            for (int t = 0; t < 8; ++t) {
+            for (int t = 0; t < 4; ++t) {
               __nv_bfloat162 v = __floats2bfloat162_rn(acc[j + t].x * rs, acc[j + t].y * rs);
-              w[t] = *reinterpret_cast<uint32_t*>(&v);
+              wv[t] = *reinterpret_cast<uint32_t*>(&v);
             }
-            st_global_v8(dst + 2 * j, w);
+            red_add_bf16x8(dst + 2 * j, wv[0], wv[1], wv[2], wv[3]);
           }
         }
       }
+      if (MODE == 1 && p.tile_arrivals) {
+        // Requantisation without a second kernel and without waiting for anybody: the N tiles of an M
+        // tile count their arrivals, and the CTA that arrives last finds every activation of the 128
+        // rows and the final row maxima in L2, turns the rows into e4m3 codes (one scale per row,
+        // max|act| / 448, solution/python/moe_fused.cu:175-195 of the reference) and writes the scales.
+        // Ordering: every promotion warp's stores -> its arrive on bar_epi (release) -> warp 0's wait
+        // (acquire) -> lane 0's acq_rel arrival on the tile counter at gpu scope; the last arriver's
+        // own arrival acquires all of them.  The counter's answer is read one item later.
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_epi);
+        if (pw == 0) {
+          bool ok = mbar_wait(bar_epi, epi_ph, abort_flag, p.status, 7);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) { alive = false; break; }
+          if (lane == 0) {
+            *last_flag = (pending_tile >= 0 && pending_prev == p.n_tiles - 1) ? (uint32_t)pending_tile + 1u : 0u;
+            pending_prev = atom_add_acq_rel_gpu(p.tile_arrivals + m_tile, 1);
+            pending_tile = m_tile;
+            mbar_arrive(bar_epi + 8);
+          }
+        }
+        bool ok2 = mbar_wait(bar_epi + 8, epi_ph, abort_flag, p.status, 8);
+        ok2 = __all_sync(0xffffffffu, ok2);
+        if (!ok2) { alive = false; break; }
+        epi_ph ^= 1u;
+        const uint32_t todo = *last_flag;
+        if (todo) requant_tile_rows(p, (int)todo - 1, pw, lane, kTileM / kPromoWarps);
+      }
       if (PROF) t_epi += clock64() - te0;
+    }
+    if (MODE == 1 && alive && p.tile_arrivals) {
+      // the verdict on this CTA's last item (no item follows that would pick it up)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_epi);
+      bool ok = true;
+      if (pw == 0) {
+        ok = mbar_wait(bar_epi, epi_ph, abort_flag, p.status, 9);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok && lane == 0) {
+          *last_flag = (pending_tile >= 0 && pending_prev == p.n_tiles - 1) ? (uint32_t)pending_tile + 1u : 0u;
+          mbar_arrive(bar_epi + 8);
+        }
+      }
+      if (ok) {
+        ok = mbar_wait(bar_epi + 8, epi_ph, abort_flag, p.status, 10);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (ok) {
+        const uint32_t todo = *last_flag;
+        if (todo) requant_tile_rows(p, (int)todo - 1, pw, lane, kTileM / kPromoWarps);
+      }
     }
     if (prof_me) {
       p.prof[0] = (unsigned long long)t_wait;                  // waiting for an accumulator
@@ -378,42 +576,55 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
-template <int MODE, int BN>
+// B200MOE_PROMO=8|16 picks the number of promotion warps (default below); read once per process.
+int promo_warps() {
+  static const int nw = [] {
+    const char* v = getenv("B200MOE_PROMO");
+    const int n = v ? atoi(v) : 0;
+    return (n == 8 || n == 16) ? n : kDefaultPromoWarps;
+  }();
+  return nw;
+}
+
+template <int MODE, int NW>
 cudaError_t launch_one(const GemmParams& p, int num_sms, cudaStream_t stream) {
   if (p.prof)
-    return launch_chained(grouped_gemm_kernel<MODE, BN, true>, dim3(num_sms), dim3(kGemmThreads),
-                          TileCfg<BN>::kSmemBytes, stream, p);
+    return launch_chained(grouped_gemm_kernel<MODE, NW, true>, dim3(num_sms), dim3(WarpCfg<NW>::kThreads), kSmemBytes,
+                          stream, p);
   else
-    return launch_chained(grouped_gemm_kernel<MODE, BN, false>, dim3(num_sms), dim3(kGemmThreads),
-                          TileCfg<BN>::kSmemBytes, stream, p);
+    return launch_chained(grouped_gemm_kernel<MODE, NW, false>, dim3(num_sms), dim3(WarpCfg<NW>::kThreads), kSmemBytes,
+                          stream, p);
 }
 
-template <int MODE, int BN>
+template <int MODE, int NW>
 cudaError_t configure_one() {
-  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BN, true>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, TileCfg<BN>::kSmemBytes);
+  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<MODE, NW, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       kSmemBytes);
   if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(grouped_gemm_kernel<MODE, BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              TileCfg<BN>::kSmemBytes);
+  return cudaFuncSetAttribute(grouped_gemm_kernel<MODE, NW, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              kSmemBytes);
 }
 
 }  // namespace
 
 cudaError_t configure_grouped_gemm() {
   cudaError_t e;
-  if ((e = configure_one<1, 128>()) != cudaSuccess) return e;
-  if ((e = configure_one<1, 256>()) != cudaSuccess) return e;
-  if ((e = configure_one<2, 128>()) != cudaSuccess) return e;
-  if ((e = configure_one<2, 256>()) != cudaSuccess) return e;
+  if ((e = configure_one<1, 8>()) != cudaSuccess) return e;
+  if ((e = configure_one<2, 8>()) != cudaSuccess) return e;
+  if ((e = configure_one<1, 16>()) != cudaSuccess) return e;
+  if ((e = configure_one<2, 16>()) != cudaSuccess) return e;
   return cudaSuccess;
 }
 
-cudaError_t launch_grouped_gemm(int mode, int bn, const GemmParams& p, int num_sms, cudaStream_t stream) {
-  if (mode == 1) return bn == 128 ? launch_one<1, 128>(p, num_sms, stream) : launch_one<1, 256>(p, num_sms, stream);
-  return bn == 128 ? launch_one<2, 128>(p, num_sms, stream) : launch_one<2, 256>(p, num_sms, stream);
+int grouped_gemm_max_kblocks() { return kMaxKBlocks; }
+
+cudaError_t launch_grouped_gemm(int mode, const GemmParams& p, int num_sms, cudaStream_t stream) {
+  const int nw = promo_warps();
+  if (mode == 1) return nw == 8 ? launch_one<1, 8>(p, num_sms, stream) : launch_one<1, 16>(p, num_sms, stream);
+  return nw == 8 ? launch_one<2, 8>(p, num_sms, stream) : launch_one<2, 16>(p, num_sms, stream);
 }
 
 }  // namespace b200moe

@@ -379,7 +379,7 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
         for (int j = 0; j < NT; ++j) {
           if (j < cnt) {
             const float rs = p.row_scale[row0 + j] * p.row_weight[row0 + j];
-            p.y[(size_t)(row0 + j) * p.hidden + col] = __float2bfloat16_rn(acc[j] * rs);
+            atomicAdd(p.out + (size_t)p.row_token[row0 + j] * p.out_stride + col, __float2bfloat16_rn(acc[j] * rs));
           }
         }
       }
@@ -423,7 +423,11 @@ cudaError_t configure_decode_gemm() {
   return configure_one<2, 64>();
 }
 
+int decode_gemm_max_kblocks() { return DCfg<16>::kMaxKBlocks; }
+
 cudaError_t launch_decode_gemm(int mode, int nt, const GemmParams& p, int num_sms, cudaStream_t stream) {
+  // the per-warp scale panels hold kMaxKBlocks entries: a longer K range would write past them
+  if (p.kblocks > DCfg<16>::kMaxKBlocks) return cudaErrorInvalidValue;
   if (mode == 1) return nt == 16 ? launch_one<1, 16>(p, num_sms, stream) : launch_one<1, 64>(p, num_sms, stream);
   return nt == 16 ? launch_one<2, 16>(p, num_sms, stream) : launch_one<2, 64>(p, num_sms, stream);
 }

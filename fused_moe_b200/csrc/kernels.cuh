@@ -58,7 +58,6 @@ struct GemmParams {
   CUtensorMap tmap_b;
   const int* meta;          // [0] = number of 128-row M tiles
   const int* tile_expert;   // expert of each M tile
-  const int* pair_tile;     // 256-row kernel: first M tile of each pair (meta[4] pairs)
   const int* row_token;     // token of each packed row, -1 for padding
   const int* expert_count;  // rows per local expert (decode kernel)
   const float* a_scale;     // GEMM1: [K/128][m_cap] activation scales
@@ -71,9 +70,13 @@ struct GemmParams {
   int hidden;
   __half* act;              // GEMM1 out: [m_cap][inter] fp16
   unsigned* row_amax;       // GEMM1 out: bits of max |act| per row
+  int* tile_arrivals;       // GEMM1: N tiles of each M tile that have stored their activations (zero at call start)
+  uint8_t* act_q_out;       // GEMM1 out (written by the CTA that completes an M tile): [m_cap][inter] e4m3
+  float* row_scale_out;     // GEMM1 out (same CTA): requantisation scale per row
   const float* row_scale;   // GEMM2 in: requantisation scale per row
   const float* row_weight;  // GEMM2 in: routing weight per row
-  __nv_bfloat16* y;         // GEMM2 out: [m_cap][hidden] bf16 rows, already scaled by weight
+  __nv_bfloat16* out;       // GEMM2 out: the layer's output rows [T][out_stride], zeroed at call start; every packed
+  long long out_stride;     //            row is added into its token's row (bf16 red.global.add)
   int* status;
   float* splitk_scratch;    // decode GEMMs: [kSplitKSlots][kSplitKMax][16][128] partial sums
   int* splitk_count;        // decode GEMMs: arrivals per weight slab, zero at kernel start and end
@@ -81,27 +84,20 @@ struct GemmParams {
   unsigned long long* trace;  // optional [64][8] absolute cycle stamps of CTA 0's first K blocks
 };
 
-// mode 1: GEMM1 + SwiGLU + row amax; mode 2: GEMM2 + weighted combine.  bn: 128 or 256.
-cudaError_t launch_grouped_gemm(int mode, int bn, const GemmParams& p, int num_sms, cudaStream_t stream);
+// mode 1: GEMM1 + SwiGLU + row amax; mode 2: GEMM2 + weighted combine.  Tiles of 128 rows x 256 weight rows.
+cudaError_t launch_grouped_gemm(int mode, const GemmParams& p, int num_sms, cudaStream_t stream);
 cudaError_t configure_grouped_gemm();   // opt-in shared memory sizes, once per process and device
-
-// The same GEMMs on CTA pairs (cta_group::2), tile 256 rows x 256 weight rows; segments must be padded to 256 rows.
-cudaError_t launch_grouped_gemm_pair(int mode, const GemmParams& p, int num_sms, cudaStream_t stream);
-cudaError_t configure_grouped_gemm_pair();
-
-// The same GEMMs with 256-row items on one CTA (gemm_m256.cu): pairs of M tiles of one expert share each B box.
-cudaError_t launch_grouped_gemm_m256(int mode, const GemmParams& p, int num_sms, cudaStream_t stream);
-cudaError_t configure_grouped_gemm_m256();
+int grouped_gemm_max_kblocks();         // largest K / 128 the kernels' scale panels hold
 
 // Decode sizes (T <= nt, nt 16 or 64): operands swapped, weights on the MMA's M side (gemm_decode.cu).
 cudaError_t launch_decode_gemm(int mode, int nt, const GemmParams& p, int num_sms, cudaStream_t stream);
 cudaError_t configure_decode_gemm();
+int decode_gemm_max_kblocks();          // largest K / 128 its per-warp scale panels hold
 
 cudaError_t launch_wait_timeout_selftest(int* status, cudaStream_t stream);
 
 cudaError_t launch_requant(const Workspace& ws, int inter, int num_sms, cudaStream_t stream);
-cudaError_t launch_combine(const Workspace& ws, int T, int hidden, void* out_bf16, long long out_row_stride,
-                           int num_sms, cudaStream_t stream);
+
 
 cudaError_t launch_ep_pack(const int32_t* ids, const float* w, const uint8_t* hidden, long long hidden_row_stride,
                            const float* hscale, long long sstride_t, long long sstride_kb, int T, int hidden_dim,

@@ -40,7 +40,7 @@ scan_kernel(Workspace ws, int e_local, int n_chunks, int pad_rows) {
       }
     }
   }
-  int padded = (total + pad_rows - 1) / pad_rows * pad_rows;   // 128, or 256 when CTA pairs run the GEMMs
+  int padded = (total + pad_rows - 1) / pad_rows * pad_rows;   // whole M tiles
   s_scan[e] = padded;
   __syncthreads();
   // inclusive Hillis-Steele scan over 256 entries
@@ -51,23 +51,8 @@ scan_kernel(Workspace ws, int e_local, int n_chunks, int pad_rows) {
     __syncthreads();
   }
   int row0 = s_scan[e] - padded;
-  // pairs of consecutive M tiles of one expert (work items of the 256-row GEMM kernel)
-  const int pairs_e = (padded / kTileM + 1) / 2;
   __syncthreads();
   const int padded_total_all = s_scan[255];
-  __syncthreads();
-  s_scan[e] = pairs_e;
-  __syncthreads();
-  for (int off = 1; off < 256; off <<= 1) {
-    int v = e >= off ? s_scan[e - off] : 0;
-    __syncthreads();
-    s_scan[e] += v;
-    __syncthreads();
-  }
-  const int pair0 = s_scan[e] - pairs_e;
-  int* pair_tile = ws.at<int>(ws.L.pair_tile);
-  for (int j = 0; j < pairs_e; ++j) pair_tile[pair0 + j] = row0 / kTileM + 2 * j;
-  const int pairs_total = s_scan[255];
   int* expert_row0 = ws.at<int>(ws.L.expert_row0);
   int* expert_count = ws.at<int>(ws.L.expert_count);
   int* tile_expert = ws.at<int>(ws.L.tile_expert);
@@ -92,7 +77,6 @@ scan_kernel(Workspace ws, int e_local, int n_chunks, int pad_rows) {
     meta[1] = padded_total;
     meta[2] = s_rows;
     meta[3] = pad_rows;
-    meta[4] = pairs_total;
   }
 }
 

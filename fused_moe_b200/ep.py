@@ -123,6 +123,27 @@ class CudaOps:
         return torch.empty(shape, dtype=dtype, device=device)
 
 
+def exchange_counts(dest_counts: torch.Tensor, fits: bool, group=None):
+    """The small all-to-all that opens an exchange through mapped buffers: rank r tells every destination
+    d how many rows it has for it, where they start in r's send buffer, and whether r's batch fitted its
+    buffers at all.  Returns (rows sent per destination, rows received per source, start of each source's
+    segment, ranks whose batch did not fit).  Every rank gets the same list of misfits from the same
+    exchange, so they all raise (or all carry on) together and no rank is left waiting in a collective.
+    Works on any backend (device tensors on NCCL, CPU tensors on gloo)."""
+    world = dist.get_world_size(group)
+    seg_off = torch.cumsum(dest_counts, 0, dtype=torch.int32) - dest_counts
+    flag = torch.full_like(dest_counts, 0 if fits else 1)
+    mine = torch.stack([dest_counts, seg_off, flag], dim=1).contiguous()    # [world, 3]
+    theirs = torch.empty_like(mine)
+    dist.all_to_all_single(theirs, mine, group=group)
+    host = torch.cat([mine, theirs]).cpu().tolist()                         # one host read
+    send_n = [int(r[0]) for r in host[:world]]
+    recv_n = [int(r[0]) for r in host[world:]]
+    recv_off = [int(r[1]) for r in host[world:]]
+    misfits = [s for s in range(world) if int(host[world + s][2]) != 0]
+    return send_n, recv_n, recv_off, misfits
+
+
 class PeerExchange:
     """Symmetric-memory buffers of one rank and their addresses in every rank (NCCL, one node)."""
 
@@ -191,9 +212,9 @@ class ExpertParallelMoE:
             if int(ok.item()) == 0:
                 self._peer, self._peer_failed = None, True
                 return None
-        if T > self._peer.cap_tokens or hidden != self._peer.hidden:
-            raise ValueError(f"{T} tokens of width {hidden} exceed the exchange buffers ({self._peer.cap_tokens} tokens "
-                             f"of width {self._peer.hidden}); pass max_tokens to ExpertParallelMoE")
+        # A batch that does not fit this rank's mapped buffers is NOT refused here: the other ranks could not
+        # know and would block in the next collective.  _forward_peer sends every rank's token count along
+        # with the row counts, and all ranks raise together (see exchange_counts).
         return self._peer
 
     def _mark(self, name: str):
@@ -279,21 +300,22 @@ class ExpertParallelMoE:
         self.last_mode = "peer"
         self._marks = []
         self._mark("start")
-        ids, w = ops.route(routing_logits, routing_bias, rsf, self.local_off, self.e_local, hidden, inter)
-        send_rows, dest_counts, send_slot = ops.pack(ids, w, hidden_states, hidden_states_scale, world,
-                                                     send_buffer=peer.send)
+        fits = T <= peer.cap_tokens and hidden == peer.hidden
+        if fits:
+            ids, w = ops.route(routing_logits, routing_bias, rsf, self.local_off, self.e_local, hidden, inter)
+            send_rows, dest_counts, send_slot = ops.pack(ids, w, hidden_states, hidden_states_scale, world,
+                                                         send_buffer=peer.send)
+        else:   # nothing of this batch may touch the mapped buffers; the ranks learn of it below
+            dest_counts = torch.zeros((world,), dtype=torch.int32, device=dev)
         self._mark("route_pack")
         # to every destination: how many rows it gets from me and where they start in my send buffer.
         # This exchange completes only after every rank's pack kernel: it is also what makes the
         # send buffers safe to read.
-        seg_off = torch.cumsum(dest_counts, 0, dtype=torch.int32) - dest_counts
-        mine = torch.stack([dest_counts, seg_off], dim=1).contiguous()          # [world, 2]
-        theirs = torch.empty_like(mine)
-        dist.all_to_all_single(theirs, mine, group=self.group)
-        host = torch.cat([mine, theirs]).cpu().tolist()                         # one host read
-        send_n = [int(r[0]) for r in host[:world]]
-        recv_n = [int(r[0]) for r in host[world:]]
-        recv_off = [int(r[1]) for r in host[world:]]
+        send_n, recv_n, recv_off, misfits = exchange_counts(dest_counts, fits, self.group)
+        if misfits:
+            raise ValueError(f"rank(s) {misfits} hold a batch that exceeds the mapped exchange buffers "
+                             f"({peer.cap_tokens} tokens of width {peer.hidden}; this rank: {T} x {hidden}); every rank "
+                             f"raises, no collective is left pending; pass max_tokens to ExpertParallelMoE")
         self.last_send_counts = send_n
         n_recv = sum(recv_n)
         self.last_recv_rows = n_recv

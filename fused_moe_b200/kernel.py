@@ -12,7 +12,14 @@ Differences a caller can observe, all documented at the boundary:
 * the result is written into a buffer owned by this module and reused by the next call
   with the same shapes, exactly as the reference does (kernel.py:251, 636) - pass
   ``out=`` to write into a tensor of your own instead;
-* shapes the CUDA library does not support raise ``MoEError`` instead of asserting.
+* shapes the CUDA library does not support raise ``MoEError`` instead of asserting;
+* calls of up to 1024 tokens are replayed as CUDA graphs: one graph per set of argument addresses
+  (what the reference does, kernel.py:613-635) and, for callers that bring fresh tensors every
+  call, one graph per SHAPE that reads the token inputs from staging buffers, so new tensors cost
+  three small device copies instead of a re-capture;
+* the device status word of every call is copied to pinned host memory behind the call and looked
+  at when the next call with the same workspace starts: a bounded device wait that ran out raises
+  ``MoEError`` there (``check_status=True`` still synchronises and raises at once).
 
 torch is used for tensors, streams and the workspace allocation only; every kernel
 is in ``libb200moe.so``.
@@ -50,6 +57,9 @@ class Workspace:
         self.ptr = (self.buffer.data_ptr() + 255) // 256 * 256
         self._skip = self.ptr - self.buffer.data_ptr()
         self.out = torch.empty((max(T, 1), hidden), dtype=torch.bfloat16, device=device)
+        # status word of the last call, copied behind it without a synchronisation (see post_status)
+        self.status_host = torch.zeros(4, dtype=torch.int32).pin_memory()
+        self._status_dev = self.buffer[self._skip:self._skip + 16].view(torch.int32)   # `status` is at offset 0
 
     def layout_of_last_call(self):
         """Offsets as the library computed them for the last call's token count (they depend
@@ -65,6 +75,18 @@ class Workspace:
         nb = n * torch.empty((), dtype=dtype).element_size()
         return self.buffer[off:off + nb].view(dtype).view(*shape)
 
+    def post_status(self):
+        """Enqueues the copy of the status word to pinned host memory on the current stream."""
+        self.status_host.copy_(self._status_dev, non_blocking=True)
+
+    def raise_if_failed(self):
+        """Looks at the last status word that has reached the host (no synchronisation)."""
+        code = int(self.status_host[0])
+        if code != 0:
+            detail = self.status_host.tolist()
+            self.status_host.zero_()
+            raise MoEError(code, "device status of an earlier b200moe_run on this workspace", f"detail={detail}")
+
     def read_status(self, stream_ptr: int = 0):
         detail = (C.c_int32 * 4)()
         code = _capi.lib().b200moe_read_status(self.ptr, stream_ptr, detail)
@@ -77,6 +99,26 @@ _workspaces: Dict[Tuple, Workspace] = {}
 GRAPH_MAX_TOKENS = 1024
 GRAPH_CACHE_ENTRIES = 64
 _graph_cache: Dict[Tuple, object] = {}
+# per shape (and weight set): how often the argument addresses were new, then the staged graph
+_staged_cache: Dict[Tuple, object] = {}
+
+
+class _StagedGraph:
+    """A captured layer call whose token inputs live in buffers of its own: a caller with new tensors
+    per call pays three device copies into them, not a new capture."""
+
+    def __init__(self, dev, T, hidden, logits, bias, scale_shape):
+        self.logits = torch.empty_like(logits)
+        self.bias = torch.empty_like(bias)
+        self.hs = torch.empty((T, hidden), dtype=torch.uint8, device=dev)
+        self.scale = torch.empty(scale_shape, dtype=torch.float32, device=dev)
+        self.graph = None
+
+    def stage(self, logits, bias, hs, scale):
+        self.logits.copy_(logits, non_blocking=True)
+        self.bias.copy_(bias, non_blocking=True)
+        self.hs.copy_(hs, non_blocking=True)
+        self.scale.copy_(scale, non_blocking=True)
 
 
 def _graphs_enabled() -> bool:
@@ -91,6 +133,7 @@ def get_workspace(device: torch.device, T: int, e_local: int, hidden: int, inter
         if ws is not None:
             cap = max(cap, 2 * ws.T if ws.T < 4096 else T)
             _graph_cache.clear()       # captured graphs point into the buffer being replaced
+            _staged_cache.clear()
             del _workspaces[key]
             del ws
         ws = Workspace(device, cap, e_local, hidden, inter)
@@ -100,6 +143,7 @@ def get_workspace(device: torch.device, T: int, e_local: int, hidden: int, inter
 
 def clear_workspaces() -> None:
     _graph_cache.clear()
+    _staged_cache.clear()
     _workspaces.clear()
 
 
@@ -207,29 +251,55 @@ def custom_kernel(routing_logits, routing_bias, hidden_states, hidden_states_sca
         ws.last_T = T
         lt, bt = _dtype_tag(logits, "routing_logits"), _dtype_tag(bias, "routing_bias")
 
-        def launch():
+        ws.raise_if_failed()
+
+        def launch(lg=logits, bs=bias, h=hs, sc=hidden_states_scale, sc_t=st_t, sc_kb=st_kb, dst=result):
             rc = _capi.lib().b200moe_run(
-                logits.data_ptr(), lt, bias.data_ptr(), bt, hs.data_ptr(), hs.stride(0),
-                hidden_states_scale.data_ptr(), st_t, st_kb,
+                lg.data_ptr(), lt, bs.data_ptr(), bt, h.data_ptr(), h.stride(0),
+                sc.data_ptr(), sc_t, sc_kb,
                 w1.data_ptr(), s1.data_ptr(), w2.data_ptr(), s2.data_ptr(),
                 T, e_local, local_off, rsf, hidden, inter,
-                ws.ptr, ws.nbytes, result.data_ptr(), result.stride(0),
+                ws.ptr, ws.nbytes, dst.data_ptr(), dst.stride(0),
                 torch.cuda.current_stream(dev).cuda_stream)
             _capi.check(rc, "b200moe_run")
+            ws.post_status()
 
         if T <= GRAPH_MAX_TOKENS and _graphs_enabled() and not torch.cuda.is_current_stream_capturing():
-            # Small batches are launch-bound: the nine launches of a call are replayed as one CUDA
-            # graph, cached per (shapes, argument addresses) like the reference (kernel.py:613-635).
-            key = (dev.index, T, e_local, hidden, inter, local_off, rsf, lt, bt, logits.data_ptr(),
-                   bias.data_ptr(), hs.data_ptr(), hs.stride(0), hidden_states_scale.data_ptr(), st_t, st_kb,
-                   w1.data_ptr(), s1.data_ptr(), w2.data_ptr(), s2.data_ptr(), ws.ptr, result.data_ptr(),
-                   result.stride(0))
+            # Small batches are launch-bound: the launches of a call are replayed as one CUDA graph.
+            shape_key = (dev.index, T, e_local, hidden, inter, local_off, rsf, lt, bt,
+                         tuple(hidden_states_scale.shape), w1.data_ptr(), s1.data_ptr(), w2.data_ptr(),
+                         s2.data_ptr(), ws.ptr)
+            key = shape_key + (logits.data_ptr(), bias.data_ptr(), hs.data_ptr(), hs.stride(0),
+                               hidden_states_scale.data_ptr(), st_t, st_kb, result.data_ptr(), result.stride(0))
             entry = _graph_cache.get(key)
-            if entry is None:
+            staged = _staged_cache.get(shape_key)
+            if entry is None and isinstance(staged, _StagedGraph):
+                # new argument addresses, known shape: copy the tokens into the staged graph's buffers
+                staged.stage(logits, bias, hs, hidden_states_scale)
+                staged.graph.replay()
+                if out is not None:
+                    result.copy_(ws.out[:T], non_blocking=True)
+            elif entry is None:
                 if len(_graph_cache) >= GRAPH_CACHE_ENTRIES:
                     _graph_cache.clear()
                 _graph_cache[key] = 1          # first sighting: run eagerly (also does the one-time set-up)
-                launch()
+                misses = (staged or 0) + 1
+                if misses >= 3:
+                    # the third set of addresses for one shape: this caller brings fresh tensors
+                    sg = _StagedGraph(dev, T, hidden, logits, bias, tuple(hidden_states_scale.shape))
+                    sg.stage(logits, bias, hs, hidden_states_scale)
+                    s_t, s_kb = _scale_strides(sg.scale, T, hidden // BLOCK)
+                    torch.cuda.synchronize(dev)
+                    sg.graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(sg.graph):
+                        launch(sg.logits, sg.bias, sg.hs, sg.scale, s_t, s_kb, ws.out[:T])
+                    _staged_cache[shape_key] = sg
+                    sg.graph.replay()
+                    if out is not None:
+                        result.copy_(ws.out[:T], non_blocking=True)
+                else:
+                    _staged_cache[shape_key] = misses
+                    launch()
             elif entry == 1:
                 graph = torch.cuda.CUDAGraph()
                 torch.cuda.synchronize(dev)
@@ -245,6 +315,7 @@ def custom_kernel(routing_logits, routing_bias, hidden_states, hidden_states_sca
         if check_status:
             code, detail = ws.read_status(stream)
             if code != 0:
+                ws.status_host.zero_()
                 raise MoEError(code, "device status after b200moe_run", f"detail={detail}")
     return result
 

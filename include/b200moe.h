@@ -62,8 +62,9 @@ typedef enum b200moe_dtype {
 typedef struct b200moe_ws_layout {
   uint64_t total_bytes;
   uint64_t status;        /* int32[16]: [0] status code, [1] detail, [2..] debug */
-  uint64_t meta;          /* int32[8]: [0] m_tiles, [1] padded rows, [2] rows with a local expert, [3] pad granularity, [4] tile pairs */
+  uint64_t meta;          /* int32[8]: [0] m_tiles, [1] padded rows, [2] rows with a local expert, [3] pad granularity */
   uint64_t splitk_count;  /* int32[2][64]: arrivals per (GEMM, weight slab) when a decode GEMM splits K; cleared per call */
+  uint64_t tile_arrivals; /* int32[max_tiles]: N tiles of each M tile whose GEMM1 epilogue has run; cleared per call */
   uint64_t chunk_counts;  /* int32[n_chunks][e_local] */
   uint64_t chunk_base;    /* int32[n_chunks][e_local] */
   uint64_t expert_count;  /* int32[e_local] */
@@ -77,13 +78,11 @@ typedef struct b200moe_ws_layout {
   uint64_t row_amax;      /* uint32[m_cap]: bits of max|act| per row */
   uint64_t act_q;         /* uint8[m_cap][inter] e4m3 */
   uint64_t row_scale;     /* float[m_cap] */
-  uint64_t y;             /* bf16[m_cap][hidden]: GEMM2 rows times routing weight */
   uint64_t tok_rows;      /* int32[T][8]: packed row of (token,k), -1 if the expert is not local */
   uint64_t topk_ids;      /* int32[T][8]  (used by b200moe_run) */
   uint64_t topk_w;        /* float[T][8]  (used by b200moe_run) */
   uint64_t trace;         /* uint64[2][64][8]: cycle stamps written when B200MOE_PROF is set */
   uint64_t splitk_scratch; /* float[64][4][16][128]: partial sums of a decode GEMM whose K range is split over CTAs */
-  uint64_t pair_tile;     /* int32[max_tiles]: first M tile of each pair of consecutive tiles of one expert (256-row items) */
   int32_t m_cap;          /* capacity in packed rows (multiple of 128) */
   int32_t max_tiles;
   int32_t n_chunks;

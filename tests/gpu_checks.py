@@ -45,8 +45,8 @@ def check_stages(inp_cpu, res, ws, act_rtol=2e-3, verbose=False):
     assert np.array_equal(counts, want_counts), "permute: per-expert counts"
     row0 = ws.view("expert_row0", torch.int32, (e_local + 1,)).cpu().numpy()
     meta = ws.view("meta", torch.int32, (8,)).cpu().numpy()
-    pad = int(meta[3])                      # 128, or 256 when CTA pairs run the GEMMs
-    assert pad in (128, 256)
+    pad = int(meta[3])                      # rows per M tile
+    assert pad == 128
     padded = (want_counts + pad - 1) // pad * pad
     assert np.array_equal(row0, np.concatenate([[0], np.cumsum(padded)])), "permute: padded segment starts"
     m_pad = int(row0[-1])

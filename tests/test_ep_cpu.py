@@ -130,3 +130,63 @@ def test_two_rank_exchange_matches_single_rank_oracle(tokens):
         assert frac_all >= 0.999, (frac_all, max_abs)
         assert max_abs < 0.13
     assert sum(ret[r][1] for r in range(world)) == total_sent
+
+
+def _misfit_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from fused_moe_b200.ep import exchange_counts
+        # rank 1's batch does not fit its buffers: it sends zero rows and the flag
+        counts = torch.tensor([3, 4], dtype=torch.int32) if rank == 0 else torch.zeros(2, dtype=torch.int32)
+        send_n, recv_n, recv_off, misfits = exchange_counts(counts, fits=(rank == 0))
+        # a second exchange right behind it shows that no collective was left half-done
+        again = exchange_counts(torch.tensor([1, 2], dtype=torch.int32), fits=True)
+        ret[rank] = (send_n, recv_n, recv_off, misfits, again[3])
+    finally:
+        dist.destroy_process_group()
+
+
+def test_batch_that_exceeds_one_ranks_buffers_is_seen_by_every_rank():
+    world = 2
+    mgr = mp.get_context("spawn").Manager()
+    ret = mgr.dict()
+    mp.spawn(_misfit_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    for r in range(world):
+        send_n, recv_n, recv_off, misfits, misfits_again = ret[r]
+        assert misfits == [1], "every rank learns which rank is over its buffers, from the same exchange"
+        assert misfits_again == []
+    assert ret[0][0] == [3, 4] and ret[0][1] == [3, 0] and ret[1][1] == [4, 0] and ret[0][2] == [0, 0]
+
+
+def _silent_rank_worker(rank, world, port, ret):
+    """Rank 1 fails on the host before it posts its counts; rank 0 must not wait for ever."""
+    import datetime
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    try:
+        from fused_moe_b200.ep import exchange_counts
+        if rank == 1:
+            ret[rank] = "left before the exchange"
+            return                      # a rank that raised or exited between steps: it never joins
+        try:
+            exchange_counts(torch.tensor([1, 1], dtype=torch.int32), fits=True)
+            ret[rank] = "returned"
+        except Exception as exc:        # gloo ends the collective with an error once the peer is gone / the limit ran out
+            ret[rank] = "error: " + type(exc).__name__
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:
+            pass
+
+
+def test_rank_that_never_posts_its_counts_ends_the_others_collective_with_an_error():
+    world = 2
+    mgr = mp.get_context("spawn").Manager()
+    ret = mgr.dict()
+    mp.spawn(_silent_rank_worker, args=(world, _free_port(), ret), nprocs=world, join=True)
+    assert ret[1] == "left before the exchange"
+    assert ret[0].startswith("error"), ret[0]

@@ -73,18 +73,23 @@ def test_benchmark_shape_against_oracle(T, tseed, zipf, full_weights_cpu, full_w
     assert frac_all >= 0.999 and frac_nz >= 0.999, (T, frac_all, frac_nz, max_abs)
 
 
-def test_run_twice_is_bit_identical_and_out_argument():
+def test_run_twice_and_out_argument():
     g, inp = golden_inputs("layer_small_T200_off64")
     dev = torch.device("cuda", 0)
     gi = inp.to(dev)
     a = K.run(*gi.args()).clone()
     b = K.run(*gi.args()).clone()
-    # stable placement, fixed K order and a per-token combine in ascending expert order: no run-to-run variation
-    assert torch.equal(a.view(torch.int16), b.view(torch.int16))
+    # stable placement and a fixed K order; only the order in which a token's (at most eight) bf16 rows are added
+    # into its output row is free.  Each addition rounds to bf16, so two orders differ by a few bf16 steps of the
+    # largest partial sum at most.
+    def close(x, y):
+        d = (x.float() - y.float()).abs()
+        return bool(d.max() <= 8 * 2.0 ** -8 * max(1.0, float(x.float().abs().max())))
+    assert close(a, b)
     own = torch.empty_like(a)
     r = K.custom_kernel(*gi.args(), out=own)
     assert r.data_ptr() == own.data_ptr()
-    assert torch.equal(own.view(torch.int16), a.view(torch.int16))
+    assert close(own, a)
 
 
 def test_scale_layouts_and_bf16_logits():
@@ -172,3 +177,22 @@ def test_bounded_wait_reports_timeout_and_leaves_the_context_usable():
     g, inp = golden_inputs("layer_small_T64_off0")
     res, ws = gpu_checks.run_gpu(inp)
     assert gpu_checks.check_stages(inp, res, ws)["frac_all"] >= 0.999
+
+
+def test_56_tokens_square_scale_tensor_is_read_kblock_major(full_weights_cpu, full_weights_gpu):
+    """T == hidden/128 == 56 makes `hidden_states_scale` square, so its shape no longer says which axis is
+    the token axis; like the reference's CUDA entry point (solution/python/moe_fused.cu:790-811) the layer
+    reads it as [K/128, T].  The scales here are far from symmetric, so the other reading would fail."""
+    inp = synth.make_inputs(T=56, seed=0, token_seed=3, weights=full_weights_cpu)
+    hsc = inp.hidden_states_scale
+    assert hsc.shape == (56, 56) and not torch.allclose(hsc, hsc.t())
+    dev = torch.device("cuda", 0)
+    gi = synth.MoEInputs(inp.routing_logits.to(dev), inp.routing_bias.to(dev), inp.hidden_states.to(dev),
+                         hsc.to(dev), *full_weights_gpu, 0, 2.5)
+    res = K.custom_kernel(*gi.args(), check_status=True)
+    ora = O.moe_layer_torch(*inp.args())
+    ws = K.get_workspace(dev, 56, 32, synth.HIDDEN, synth.INTER)
+    assert np.array_equal(ws.view("topk_ids", torch.int32, (56, 8)).cpu().numpy(), ora["ids"])
+    frac_all, frac_nz, max_abs = synth.check_close(res, ora["out"])
+    assert frac_all >= 0.999 and frac_nz >= 0.999, (frac_all, frac_nz, max_abs)
+    assert synth.contest_match(res, ora["out"]) >= 0.999
