@@ -32,7 +32,7 @@ class MoEError(RuntimeError):
 
 class WsLayout(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in (
-        "total_bytes", "status", "meta", "splitk_count", "tile_arrivals", "chunk_counts", "chunk_base", "expert_count",
+        "total_bytes", "status", "meta", "splitk_count", "chunk_counts", "chunk_base", "expert_count",
         "expert_row0", "tile_expert", "row_token", "row_weight", "a_packed", "a_scale", "act",
         "row_amax", "act_q", "row_scale", "tok_rows", "topk_ids", "topk_w", "trace", "splitk_scratch")] + [
         (n, C.c_int32) for n in ("m_cap", "max_tiles", "n_chunks", "chunk_tokens")]

@@ -149,7 +149,6 @@ void compute_layout(int T, int e_local, int hidden, int inter, b200moe_ws_layout
   L->status = take(16 * 4);
   L->meta = take(8 * 4);
   L->splitk_count = take(2 * kSplitKSlots * 4);   // inside the range that clear_counters() zeroes
-  L->tile_arrivals = take((uint64_t)L->max_tiles * 4);   // likewise
   L->chunk_counts = take((uint64_t)n_chunks * e_local * 4);
   L->chunk_base = take((uint64_t)n_chunks * e_local * 4);
   L->expert_count = take((uint64_t)e_local * 4);
@@ -184,7 +183,7 @@ int bind_workspace(int T, int e_local, int hidden, int inter, void* workspace, s
 
 // Clears the status word and the histogram (start of a layer call).
 int clear_counters(const Workspace& ws, int e_local, cudaStream_t stream) {
-  // status, meta, splitk_count, tile_arrivals, chunk_counts are adjacent: one memset covers them
+  // status, meta, splitk_count, chunk_counts are adjacent: one memset covers them
   size_t bytes = (size_t)(ws.L.chunk_counts - ws.L.status) + (size_t)ws.L.n_chunks * e_local * 4;
   CUDA_TRY(cudaMemsetAsync(ws.base + ws.L.status, 0, bytes, stream));
   return B200MOE_OK;
@@ -359,14 +358,6 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
   g1.hidden = hidden;
   g1.act = ws.at<__half>(ws.L.act);
   g1.row_amax = ws.at<unsigned>(ws.L.row_amax);
-  // B200MOE_FUSED_REQUANT=1: the CTA that completes an M tile in GEMM1 requantises it (default: a kernel of its own)
-  static const bool fused_requant = [] {
-    const char* v = getenv("B200MOE_FUSED_REQUANT");
-    return v && v[0] == '1';
-  }();
-  g1.tile_arrivals = fused_requant ? ws.at<int>(ws.L.tile_arrivals) : nullptr;
-  g1.act_q_out = ws.at<uint8_t>(ws.L.act_q);
-  g1.row_scale_out = ws.at<float>(ws.L.row_scale);
   g1.status = ws.at<int>(ws.L.status);
   g1.splitk_scratch = ws.at<float>(ws.L.splitk_scratch);
   g1.splitk_count = ws.at<int>(ws.L.splitk_count);
@@ -384,8 +375,7 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
     if (stop) CUDA_TRY(cudaEventRecord(stop, st));
   }
 
-  // the 128-row tiles requantise inside GEMM1 (the CTA that completes an M tile); the decode kernels do not
-  if (nt || !fused_requant) CUDA_TRY(launch_requant(ws, inter, num_sms, st));
+  CUDA_TRY(launch_requant(ws, inter, num_sms, st));
 
   GemmParams g2;
   memset(&g2, 0, sizeof(g2));

@@ -5,17 +5,19 @@
 // of its `swiglu_fp8_requant_kernel` (solution/python/moe_fused.cu:131-196) and the
 // per-row scaling of its combine kernels (moe_fused.cu:346-393, 490-517).
 //
-// One CTA of 20 warps per SM walks work items (M tile of 128 packed rows, N tile of 256
+// One CTA of 12 warps per SM walks work items (M tile of 128 packed rows, N tile of 256
 // weight rows).  Per 128-wide K block (= one fp32 scale block, = one 128-byte swizzled row):
 //   warps 0, 3   TMA producers (one lane each, alternate K blocks): A box 128x128 B, one B box
 //                256x128 B and (GEMM1) the 128 activation scales of the K block into a smem ring
 //   warps 1, 2   MMA issuers (one lane each, alternate K blocks, issuer i always writes TMEM
 //                accumulator i): 4 tcgen05.mma (K=32 each) starting from zero, so an accumulator
 //                holds the raw e4m3 dot product of ONE K block
-//   warps 4-19   promotion: 16 warps, four per TMEM lane quarter, 64 accumulator columns each;
-//                they read the K block's partial sums back (tcgen05.ld) and fold them into fp32
-//                registers with packed FMAs: acc += (a_scale * b_scale) * partial.  The block
-//                scales are arbitrary (signed) fp32 numbers, so they cannot ride on the MMA.
+//   warps 4-11   promotion: two warps per TMEM lane quarter, 128 accumulator columns each; they
+//                read the K block's partial sums back (tcgen05.ld, two loads in flight) and fold
+//                them into fp32 registers with packed FMAs: acc += (a_scale * b_scale) * partial.
+//                The block scales are arbitrary (signed) fp32 numbers, so they cannot ride on the
+//                MMA.  (Sixteen warps with 64 columns each fit only 112 registers per thread and
+//                measured slower.)
 // What shaped the hand-offs: an mbarrier wait costs ~180 cycles of latency even when the phase
 // is already complete, a single thread needs ~360 cycles to issue a K block's MMAs and commits,
 // and the promotion warps are the busiest role.  Therefore
@@ -26,8 +28,11 @@
 //   * activation scales arrive in shared memory with the operands (same barrier), weight scales
 //     of an item sit in a per-warp panel, so the K loop touches no global memory.
 // GEMM1 pairs gate rows [n, n+128) with up rows [inter+n, ...) in one tile, so the epilogue
-// computes g*silu(u) in registers, stores fp16 activations and the row maximum; the CTA that
-// finishes the last N tile of an M tile requantises the tile's rows to e4m3 (no second kernel).
+// computes g*silu(u) in registers, stores fp16 activations and the row maximum.  (Requantising
+// inside this kernel - the CTA that completes the last N tile of an M tile turning the tile's rows
+// into e4m3 - was built and measured: read back at once it costs every item an atomic round trip,
+// read back one item later the rows have left L2 and the lone CTA waits on HBM latency, 2.5 ms per
+// step at 256 experts; the row scale needs all 16 N tiles, so the requantisation stays a kernel.)
 // GEMM2's epilogue multiplies by (row requant scale * routing weight) and adds the bf16 row into its
 // token's row of the output (red.global.add.noftz.v4.bf16x2): no second pass over the rows.
 //
@@ -43,26 +48,18 @@ namespace b200moe {
 namespace {
 
 constexpr int kCtrlWarps = 4;
-// Register budget: the CTA owns what it was launched with (threads x launch registers) and
-// setmaxnreg only moves registers inside that pool - an increase that the pool cannot serve blocks
-// for ever.  NW promotion warps: 8 (128 accumulator columns per thread) or 16 (64 per thread).
-template <int NW> struct WarpCfg;
-template <> struct WarpCfg<8> {
-  static constexpr int kThreads = 32 * (kCtrlWarps + 8);   // 384
-  static constexpr int kLaunchRegs = 168, kCtrlRegs = 56, kPromoRegs = 224;
-};
-template <> struct WarpCfg<16> {
-  static constexpr int kThreads = 32 * (kCtrlWarps + 16);  // 640
-  static constexpr int kLaunchRegs = 96, kCtrlRegs = 32, kPromoRegs = 112;
-};
-template <int NW> constexpr bool reg_budget_ok() {
-  using W = WarpCfg<NW>;
-  return 32 * kCtrlWarps * (W::kLaunchRegs - W::kCtrlRegs) >= 32 * NW * (W::kPromoRegs - W::kLaunchRegs) &&
-         W::kThreads * W::kLaunchRegs <= 65536 && W::kThreads * (W::kLaunchRegs + 8) > 65536;
-}
-static_assert(reg_budget_ok<8>() && reg_budget_ok<16>(), "setmaxnreg.inc would wait for registers that nobody releases");
-constexpr int kMaxPromoWarps = 16;
-constexpr int kDefaultPromoWarps = 8;
+constexpr int kPromoWarps = 8;
+constexpr int kGemmThreads = 32 * (kCtrlWarps + kPromoWarps);   // 384: three warpgroups
+// Register budget: the CTA owns what it was launched with, 384 threads x 168 registers, and
+// setmaxnreg only moves registers inside that pool (an increase that the pool cannot serve blocks
+// for ever): 128 control threads give up 168 - 56 each, 256 promotion threads take 224 - 168 each.
+constexpr int kLaunchRegs = 168;
+constexpr int kCtrlRegs = 56;
+constexpr int kPromoRegs = 224;
+static_assert(32 * kCtrlWarps * (kLaunchRegs - kCtrlRegs) >= 32 * kPromoWarps * (kPromoRegs - kLaunchRegs),
+              "setmaxnreg.inc would wait for registers that nobody releases");
+static_assert(kGemmThreads * kLaunchRegs <= 65536 && kGemmThreads * (kLaunchRegs + 8) > 65536,
+              "kLaunchRegs must be what 384 threads per SM are launched with");
 constexpr int kBN = 256;
 constexpr int kABytes = kTileM * kBlockK;   // 16 KiB
 constexpr int kBBytes = kBN * kBlockK;      // 32 KiB
@@ -71,7 +68,7 @@ constexpr int kStages = 4;
 constexpr int kRing = 8;                    // activation-scale slots; see the reuse argument at the producer
 constexpr int kRingBytes = kRing * kTileM * 4;
 constexpr int kPanelFloats = 128;           // per promotion warp: two runs of up to 64 weight scales
-constexpr int kPanelBytes = kMaxPromoWarps * kPanelFloats * 4;
+constexpr int kPanelBytes = kPromoWarps * kPanelFloats * 4;
 constexpr int kMaxKBlocks = 64;
 constexpr int kBarBytes = 256;
 constexpr int kSmemBytes = kStages * kStageBytes + kRingBytes + kPanelBytes + kBarBytes + 1024;   // + alignment slack
@@ -82,20 +79,12 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   return g * (u * sig);
 }
 
-// acc[16 pairs] += scale * r[32]
+// acc[16 pairs] += scale * r[32] with packed fp32 FMAs (scalar FMAs measured the same)
 __device__ __forceinline__ void fma_chunk(float2* acc, const uint32_t (&r)[32], float sc) {
-#ifdef B200MOE_SCALAR_FMA
-#pragma unroll
-  for (int j = 0; j < 16; ++j) {
-    acc[j].x = fmaf(__uint_as_float(r[2 * j]), sc, acc[j].x);
-    acc[j].y = fmaf(__uint_as_float(r[2 * j + 1]), sc, acc[j].y);
-  }
-#else
   const float2 s2 = make_float2(sc, sc);
 #pragma unroll
   for (int j = 0; j < 16; ++j)
     acc[j] = __ffma2_rn(make_float2(__uint_as_float(r[2 * j]), __uint_as_float(r[2 * j + 1])), s2, acc[j]);
-#endif
 }
 
 // untiled bulk copy global -> shared (16-byte aligned, size a multiple of 16), counted on an mbarrier
@@ -113,11 +102,6 @@ __device__ __forceinline__ uint32_t ld_acquire_smem(uint32_t addr) {
   uint32_t v;
   asm volatile("ld.acquire.cta.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
   return v;
-}
-__device__ __forceinline__ int atom_add_acq_rel_gpu(int* addr, int v) {
-  int old;
-  asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], %2;" : "=r"(old) : "l"(addr), "r"(v) : "memory");
-  return old;
 }
 __device__ __forceinline__ float ld_smem_f32(uint32_t addr) {
   float v;
@@ -151,49 +135,11 @@ __device__ __forceinline__ bool counter_wait(uint32_t addr, uint32_t target, vol
   }
 }
 
-// e4m3 codes and scales of the rows of M tile `m_tile` that promotion warp `pw` owns, from the fp16
-// activations and row maxima that the tile's 16 CTAs left in L2 (called by the CTA that arrived last).
-// Not inlined: its registers must not add to the K loop's.
-__device__ __noinline__ void requant_tile_rows(const GemmParams& p, int m_tile, int pw, int lane, int rows_per_warp) {
-  const int vecs = p.inter / 8;   // 8 halves = 16 bytes in, 8 bytes out
-  for (int r8 = 0; r8 < rows_per_warp; ++r8) {
-    const int m = m_tile * kTileM + pw * rows_per_warp + r8;
-    if (p.row_token[m] < 0) continue;
-    const float amax = fmaxf(__uint_as_float(__ldcg(p.row_amax + m)), 1e-8f);
-    const float sc = fmaxf(amax / 448.0f, 1e-8f);
-    if (lane == 0) p.row_scale_out[m] = sc;
-    const uint4* src = reinterpret_cast<const uint4*>(p.act + (size_t)m * p.inter);
-    uint2* dstq = reinterpret_cast<uint2*>(p.act_q_out + (size_t)m * p.inter);
-    for (int v0 = 0; v0 < vecs; v0 += 128) {
-      uint4 raw[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (v0 + u * 32 + lane < vecs) raw[u] = __ldcg(src + v0 + u * 32 + lane);
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        if (v0 + u * 32 + lane >= vecs) continue;
-        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw[u].x));
-        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw[u].y));
-        const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&raw[u].z));
-        const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&raw[u].w));
-        uint2 pk;
-        pk.x = pack4_e4m3(a.x / sc, a.y / sc, b.x / sc, b.y / sc);
-        pk.y = pack4_e4m3(c.x / sc, c.y / sc, d.x / sc, d.y / sc);
-        dstq[v0 + u * 32 + lane] = pk;
-      }
-    }
-  }
-}
-
-template <int MODE, int NW, bool PROF>
-__global__ void __launch_bounds__(WarpCfg<NW>::kThreads, 1)
+template <int MODE, bool PROF>
+__global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   constexpr int S = kStages;
-  constexpr int kPromoWarps = NW;
-  constexpr int kCtrlRegs = WarpCfg<NW>::kCtrlRegs, kPromoRegs = WarpCfg<NW>::kPromoRegs;
-  constexpr int CH = 32 / NW;          // 32-column chunks per promotion thread: 256 columns / (NW / 4 warps per quarter) / 32
-  static_assert(CH == 2 || CH == 4, "promotion threads hold two or four 32-column chunks");
-  constexpr int WQ = NW / 4;           // promotion warps per TMEM lane quarter
+  constexpr int CH = 4;                // 32-column chunks per promotion thread: 256 columns / 2 warps per lane quarter / 32
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t smem_base = smem_u32(smem);
@@ -204,8 +150,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   const uint32_t bar_empty = bar_full + 8 * S;           // S barriers: stage consumed by the MMAs
   const uint32_t bar_tfull = bar_empty + 8 * S;          // 2 barriers: accumulator written
   const uint32_t bar_drain = bar_tfull + 16;             // 2 barriers: each issuer's MMAs retired (teardown)
-  const uint32_t bar_epi = bar_drain + 16;               // 2 barriers: GEMM1 tile epilogue (all stored; verdict known)
-  uint32_t* words = reinterpret_cast<uint32_t*>(bars + 2 * S + 6);
+  uint32_t* words = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
   const uint32_t cnt_read = smem_u32(words);             // 2 counters: promotion warps that read accumulator b back
   uint32_t* tmem_slot = words + 2;
   volatile int* abort_flag = reinterpret_cast<volatile int*>(words + 3);
@@ -222,8 +167,6 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     mbar_init(bar_tfull + 8, 1);
     mbar_init(bar_drain, 1);
     mbar_init(bar_drain + 8, 1);
-    mbar_init(bar_epi, kPromoWarps);
-    mbar_init(bar_epi + 8, 1);
     words[0] = 0;
     words[1] = 0;
     abort_flag[0] = 0;
@@ -257,6 +200,9 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       // it - 4 have completed (the stage's "empty" barrier).  Its last readers, the promotion warps of
       // K block it - 8, read their scale before they released that accumulator, i.e. before the MMAs
       // of K block it - 6 could start.
+      // (Pulling weight boxes into L2 ahead of their copy - by the TMA unit or by prefetch.global.L2 from
+      // spare lanes, 2 to 24 K blocks ahead - and L2 eviction hints on the copies were all measured: every
+      // form of look-ahead made the streaming case slower, the hints changed nothing.)
       const uint32_t pme = warp == 0 ? 0u : 1u;
       uint32_t it = 0;
       bool alive = true;
@@ -266,20 +212,20 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         // GEMM1: first row inside the gate (and up) plane of expert e; GEMM2: row of [e_local*hidden][inter]
         const int brow = MODE == 1 ? n_tile * (kBN / 2) : e * p.n_per_expert + n_tile * kBN;
         for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          if ((it & 1u) == pme) {
-            const uint32_t s = it % S, ph = (it / S) & 1u;
-            if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status, 1)) { alive = false; break; }
-            const uint32_t full = bar_full + 8 * s;
-            const uint32_t a_dst = smem_base + s * kStageBytes;
-            mbar_arrive_expect_tx(full, kStageBytes + (MODE == 1 ? kTileM * 4 : 0));
-            tma_load_2d(a_dst, &p.tmap_a, kb * kBlockK, m_tile * kTileM, full);
-            // the whole B tile in one operation: 128 gate rows + 128 up rows (3D box over the two planes), or 256 rows
-            if (MODE == 1) tma_load_3d(a_dst + kABytes, &p.tmap_b, kb * kBlockK, brow, 2 * e, full);
-            else tma_load_2d(a_dst + kABytes, &p.tmap_b, kb * kBlockK, brow, full);
-            if (MODE == 1)
-              bulk_load(ring_base + (it % kRing) * (kTileM * 4),
-                        p.a_scale + (size_t)kb * p.m_cap + (size_t)m_tile * kTileM, kTileM * 4, full);
-          }
+          if ((it & 1u) != pme) continue;
+          const uint32_t s = it % S, ph = (it / S) & 1u;
+          if (!mbar_wait(bar_empty + 8 * s, ph ^ 1u, abort_flag, p.status, 1)) { alive = false; break; }
+          const uint32_t full = bar_full + 8 * s;
+          const uint32_t a_dst = smem_base + s * kStageBytes;
+          mbar_arrive_expect_tx(full, kStageBytes + (MODE == 1 ? kTileM * 4 : 0));
+          // the whole B tile in one operation: 128 gate rows + 128 up rows (3D box over the two planes), or 256
+          // rows; first, because it is the part that comes from HBM
+          if (MODE == 1) tma_load_3d(a_dst + kABytes, &p.tmap_b, kb * kBlockK, brow, 2 * e, full);
+          else tma_load_2d(a_dst + kABytes, &p.tmap_b, kb * kBlockK, brow, full);
+          tma_load_2d(a_dst, &p.tmap_a, kb * kBlockK, m_tile * kTileM, full);
+          if (MODE == 1)
+            bulk_load(ring_base + (it % kRing) * (kTileM * 4),
+                      p.a_scale + (size_t)kb * p.m_cap + (size_t)m_tile * kTileM, kTileM * 4, full);
         }
       }
       // Copies still in flight must land before the CTA's shared memory is released.
@@ -305,7 +251,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           // left on the critical path.
           if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 3)) { alive = false; break; }
           const long long m1 = PROF ? clock64() : 0;
-          // use number it/2 of accumulator `me`: all 16 promotion warps have read the previous one
+          // use number it/2 of accumulator `me`: all promotion warps have read the previous one
           if (!counter_wait(cnt_read + 4 * me, (uint32_t)kPromoWarps * (it >> 1), abort_flag, p.status, 2)) {
             alive = false;
             break;
@@ -339,7 +285,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     reg_alloc<kPromoRegs>();
     const int pw = warp - kCtrlWarps;
     const int q = pw & 3;          // TMEM lane quarter this warp may read (= warp % 4)
-    const int cg = pw >> 2;        // which 256 / WQ of the tile's accumulator columns
+    const int cg = pw >> 2;        // which half of the tile's 256 accumulator columns
     constexpr int HC = CH / 2;     // chunks per half (GEMM1: gate half, up half)
     // GEMM1: HC x 32 gate columns and the matching up columns; GEMM2: CH x 32 consecutive columns.
     // chunk c < HC sits at col_lo + 32 c, chunk c >= HC at col_hi + 32 (c - HC)
@@ -354,11 +300,6 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     long long t_wait = 0, t_promote = 0, t_epi = 0;
     const int nblk_per_expert = p.n_per_expert / kBlockK;
     uint32_t peek = 0;   // "accumulator written" of the coming K block already seen complete
-    uint32_t epi_ph = 0;  // phase of the two epilogue barriers (GEMM1)
-    volatile uint32_t* last_flag = words + 5;   // 0, or 1 + the M tile this CTA has to requantise
-    // GEMM1, lane 0 of promotion warp 0: this CTA's arrival on its previous item's M tile (the atomic's
-    // answer is looked at one item later, so nobody waits for it)
-    int pending_tile = -1, pending_prev = 0;
     for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x) {
       const int m_tile = w / p.n_tiles, n_tile = w % p.n_tiles;
       const int e = p.tile_expert[m_tile];
@@ -430,20 +371,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
         // picked up after the last FMAs, so its latency costs nothing, and when it says "written" the
         // next iteration starts without a wait.  (Past the CTA's last K block nothing consumes it.)
         uint32_t pk;
-        if constexpr (CH == 2) {
-          uint32_t ra[32];
-          tmem_ld_32x32(t_row + col_lo, ra);
-          load_scales();
-          tmem_ld_wait_on(ra);
-          fma_chunk(acc, ra, sc0);
-          tmem_ld_32x32(t_row + col_hi, ra);
-          tmem_ld_wait_on(ra);
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) red_add_smem(cnt_read + 4 * b, 1u);
-          pk = mbar_test_wait(bar_tfull + 8 * (nit & 1u), (nit >> 1) & 1u);
-          fma_chunk(acc + 16, ra, sc1);
-        } else {
+        {
           uint32_t ra[32], rb[32];
           tmem_ld_32x32(t_row + col_lo, ra);
           tmem_ld_32x32(t_row + col_lo + 32, rb);
@@ -513,57 +441,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           }
         }
       }
-      if (MODE == 1 && p.tile_arrivals) {
-        // Requantisation without a second kernel and without waiting for anybody: the N tiles of an M
-        // tile count their arrivals, and the CTA that arrives last finds every activation of the 128
-        // rows and the final row maxima in L2, turns the rows into e4m3 codes (one scale per row,
-        // max|act| / 448, solution/python/moe_fused.cu:175-195 of the reference) and writes the scales.
-        // Ordering: every promotion warp's stores -> its arrive on bar_epi (release) -> warp 0's wait
-        // (acquire) -> lane 0's acq_rel arrival on the tile counter at gpu scope; the last arriver's
-        // own arrival acquires all of them.  The counter's answer is read one item later.
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_epi);
-        if (pw == 0) {
-          bool ok = mbar_wait(bar_epi, epi_ph, abort_flag, p.status, 7);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) { alive = false; break; }
-          if (lane == 0) {
-            *last_flag = (pending_tile >= 0 && pending_prev == p.n_tiles - 1) ? (uint32_t)pending_tile + 1u : 0u;
-            pending_prev = atom_add_acq_rel_gpu(p.tile_arrivals + m_tile, 1);
-            pending_tile = m_tile;
-            mbar_arrive(bar_epi + 8);
-          }
-        }
-        bool ok2 = mbar_wait(bar_epi + 8, epi_ph, abort_flag, p.status, 8);
-        ok2 = __all_sync(0xffffffffu, ok2);
-        if (!ok2) { alive = false; break; }
-        epi_ph ^= 1u;
-        const uint32_t todo = *last_flag;
-        if (todo) requant_tile_rows(p, (int)todo - 1, pw, lane, kTileM / kPromoWarps);
-      }
       if (PROF) t_epi += clock64() - te0;
-    }
-    if (MODE == 1 && alive && p.tile_arrivals) {
-      // the verdict on this CTA's last item (no item follows that would pick it up)
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_epi);
-      bool ok = true;
-      if (pw == 0) {
-        ok = mbar_wait(bar_epi, epi_ph, abort_flag, p.status, 9);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok && lane == 0) {
-          *last_flag = (pending_tile >= 0 && pending_prev == p.n_tiles - 1) ? (uint32_t)pending_tile + 1u : 0u;
-          mbar_arrive(bar_epi + 8);
-        }
-      }
-      if (ok) {
-        ok = mbar_wait(bar_epi + 8, epi_ph, abort_flag, p.status, 10);
-        ok = __all_sync(0xffffffffu, ok);
-      }
-      if (ok) {
-        const uint32_t todo = *last_flag;
-        if (todo) requant_tile_rows(p, (int)todo - 1, pw, lane, kTileM / kPromoWarps);
-      }
     }
     if (prof_me) {
       p.prof[0] = (unsigned long long)t_wait;                  // waiting for an accumulator
@@ -579,32 +457,20 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
 }
 
-// B200MOE_PROMO=8|16 picks the number of promotion warps (default below); read once per process.
-int promo_warps() {
-  static const int nw = [] {
-    const char* v = getenv("B200MOE_PROMO");
-    const int n = v ? atoi(v) : 0;
-    return (n == 8 || n == 16) ? n : kDefaultPromoWarps;
-  }();
-  return nw;
-}
-
-template <int MODE, int NW>
+template <int MODE>
 cudaError_t launch_one(const GemmParams& p, int num_sms, cudaStream_t stream) {
   if (p.prof)
-    return launch_chained(grouped_gemm_kernel<MODE, NW, true>, dim3(num_sms), dim3(WarpCfg<NW>::kThreads), kSmemBytes,
-                          stream, p);
+    return launch_chained(grouped_gemm_kernel<MODE, true>, dim3(num_sms), dim3(kGemmThreads), kSmemBytes, stream, p);
   else
-    return launch_chained(grouped_gemm_kernel<MODE, NW, false>, dim3(num_sms), dim3(WarpCfg<NW>::kThreads), kSmemBytes,
-                          stream, p);
+    return launch_chained(grouped_gemm_kernel<MODE, false>, dim3(num_sms), dim3(kGemmThreads), kSmemBytes, stream, p);
 }
 
-template <int MODE, int NW>
+template <int MODE>
 cudaError_t configure_one() {
-  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<MODE, NW, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(grouped_gemm_kernel<MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        kSmemBytes);
   if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(grouped_gemm_kernel<MODE, NW, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  return cudaFuncSetAttribute(grouped_gemm_kernel<MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               kSmemBytes);
 }
 
@@ -612,19 +478,14 @@ cudaError_t configure_one() {
 
 cudaError_t configure_grouped_gemm() {
   cudaError_t e;
-  if ((e = configure_one<1, 8>()) != cudaSuccess) return e;
-  if ((e = configure_one<2, 8>()) != cudaSuccess) return e;
-  if ((e = configure_one<1, 16>()) != cudaSuccess) return e;
-  if ((e = configure_one<2, 16>()) != cudaSuccess) return e;
-  return cudaSuccess;
+  if ((e = configure_one<1>()) != cudaSuccess) return e;
+  return configure_one<2>();
 }
 
 int grouped_gemm_max_kblocks() { return kMaxKBlocks; }
 
 cudaError_t launch_grouped_gemm(int mode, const GemmParams& p, int num_sms, cudaStream_t stream) {
-  const int nw = promo_warps();
-  if (mode == 1) return nw == 8 ? launch_one<1, 8>(p, num_sms, stream) : launch_one<1, 16>(p, num_sms, stream);
-  return nw == 8 ? launch_one<2, 8>(p, num_sms, stream) : launch_one<2, 16>(p, num_sms, stream);
+  return mode == 1 ? launch_one<1>(p, num_sms, stream) : launch_one<2>(p, num_sms, stream);
 }
 
 }  // namespace b200moe

@@ -70,9 +70,6 @@ struct GemmParams {
   int hidden;
   __half* act;              // GEMM1 out: [m_cap][inter] fp16
   unsigned* row_amax;       // GEMM1 out: bits of max |act| per row
-  int* tile_arrivals;       // GEMM1: N tiles of each M tile that have stored their activations (zero at call start)
-  uint8_t* act_q_out;       // GEMM1 out (written by the CTA that completes an M tile): [m_cap][inter] e4m3
-  float* row_scale_out;     // GEMM1 out (same CTA): requantisation scale per row
   const float* row_scale;   // GEMM2 in: requantisation scale per row
   const float* row_weight;  // GEMM2 in: routing weight per row
   __nv_bfloat16* out;       // GEMM2 out: the layer's output rows [T][out_stride], zeroed at call start; every packed

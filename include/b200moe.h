@@ -64,7 +64,6 @@ typedef struct b200moe_ws_layout {
   uint64_t status;        /* int32[16]: [0] status code, [1] detail, [2..] debug */
   uint64_t meta;          /* int32[8]: [0] m_tiles, [1] padded rows, [2] rows with a local expert, [3] pad granularity */
   uint64_t splitk_count;  /* int32[2][64]: arrivals per (GEMM, weight slab) when a decode GEMM splits K; cleared per call */
-  uint64_t tile_arrivals; /* int32[max_tiles]: N tiles of each M tile whose GEMM1 epilogue has run; cleared per call */
   uint64_t chunk_counts;  /* int32[n_chunks][e_local] */
   uint64_t chunk_base;    /* int32[n_chunks][e_local] */
   uint64_t expert_count;  /* int32[e_local] */
