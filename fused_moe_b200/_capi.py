@@ -32,7 +32,7 @@ class MoEError(RuntimeError):
 
 class WsLayout(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in (
-        "total_bytes", "status", "meta", "splitk_count", "chunk_counts", "chunk_base", "expert_count",
+        "total_bytes", "status", "meta", "splitk_count", "tile_done", "chunk_counts", "chunk_base", "expert_count",
         "expert_row0", "tile_expert", "row_token", "row_weight", "a_packed", "a_scale", "act",
         "row_amax", "act_q", "row_scale", "tok_rows", "topk_ids", "topk_w", "trace", "splitk_scratch")] + [
         (n, C.c_int32) for n in ("m_cap", "max_tiles", "n_chunks", "chunk_tokens")]
@@ -55,6 +55,7 @@ SIGNATURES = {
     "b200moe_run": (_I, [_P, _I, _P, _I, _P, _L, _P, _L, _L, _P, _P, _P, _P,
                          _I, _I, _I, _F, _I, _I, _P, _Z, _P, _L, _P]),
     "b200moe_read_status": (_I, [_P, _P, C.POINTER(C.c_int32)]),
+    "b200moe_set_status_mirror": (_I, [_P]),
     "b200moe_profile_next_gemm1": (_I, [_P, _P]),
     "b200moe_selftest_wait_timeout": (_I, [_P, _P]),
     "b200moe_launches_per_run": (_I, [_I, _I]),

@@ -46,6 +46,10 @@ struct DeviceInfo {
 thread_local cudaEvent_t g_prof_start = nullptr;
 thread_local cudaEvent_t g_prof_stop = nullptr;
 
+// Optional host-mapped int32[4] of this thread's calls: a kernel that gives up on a bounded wait copies the
+// status word there, so a host can notice without a device-to-host copy per call.
+thread_local int* g_status_mirror = nullptr;
+
 std::mutex g_mutex;
 EncodeTiledFn g_encode = nullptr;
 DeviceInfo g_dev[64];
@@ -149,6 +153,7 @@ void compute_layout(int T, int e_local, int hidden, int inter, b200moe_ws_layout
   L->status = take(16 * 4);
   L->meta = take(8 * 4);
   L->splitk_count = take(2 * kSplitKSlots * 4);   // inside the range that clear_counters() zeroes
+  L->tile_done = take((uint64_t)L->max_tiles * 4);   // likewise
   L->chunk_counts = take((uint64_t)n_chunks * e_local * 4);
   L->chunk_base = take((uint64_t)n_chunks * e_local * 4);
   L->expert_count = take((uint64_t)e_local * 4);
@@ -183,7 +188,7 @@ int bind_workspace(int T, int e_local, int hidden, int inter, void* workspace, s
 
 // Clears the status word and the histogram (start of a layer call).
 int clear_counters(const Workspace& ws, int e_local, cudaStream_t stream) {
-  // status, meta, splitk_count, chunk_counts are adjacent: one memset covers them
+  // status, meta, splitk_count, tile_done, chunk_counts are adjacent: one memset covers them
   size_t bytes = (size_t)(ws.L.chunk_counts - ws.L.status) + (size_t)ws.L.n_chunks * e_local * 4;
   CUDA_TRY(cudaMemsetAsync(ws.base + ws.L.status, 0, bytes, stream));
   return B200MOE_OK;
@@ -219,6 +224,11 @@ int b200moe_workspace_layout(int T, int e_local, int hidden, int inter, b200moe_
   return B200MOE_OK;
 }
 
+int b200moe_set_status_mirror(void* host_mapped_int4) {
+  g_status_mirror = reinterpret_cast<int*>(host_mapped_int4);
+  return B200MOE_OK;
+}
+
 int b200moe_profile_next_gemm1(void* start_event, void* stop_event) {
   g_prof_start = reinterpret_cast<cudaEvent_t>(start_event);
   g_prof_stop = reinterpret_cast<cudaEvent_t>(stop_event);
@@ -230,8 +240,8 @@ int b200moe_launches_per_run(int T, int e_local) {
   if (T <= 0) return 0;
   const char* front = getenv("B200MOE_FRONT");
   const bool fused_front = T <= kFrontSmallMaxTokens && !(front && front[0] == '0');
-  // route, scan, place, gather, gemm1, [requant], gemm2 (+ weighted unpermute / reduce into the output); calls of at
-  // most 32 tokens fuse the first three
+  // route, scan, place, gather, gemm1, requant, gemm2 (+ weighted unpermute / reduce into the output); calls of at
+  // most 32 tokens fuse the first three, the decode GEMM1 (at most 16 tokens) also requantises
   static const bool decode_on = [] {
     const char* v = getenv("B200MOE_DECODE");
     return !(v && v[0] == '0');
@@ -240,9 +250,8 @@ int b200moe_launches_per_run(int T, int e_local) {
     const char* v = getenv("B200MOE_DECODE");
     return (v && v[0] == '6') ? 64 : 16;
   }();
-  (void)decode_on;
-  (void)decode_max_t;
-  return (fused_front ? 4 : 6) + 1;
+  const int requant = (decode_on && T <= decode_max_t) ? 0 : 1;   // decode GEMM1 requantises by itself
+  return (fused_front ? 4 : 6) + requant;
 }
 
 int b200moe_route(const void* logits, int logits_dtype, const void* bias, int bias_dtype, int T,
@@ -314,12 +323,10 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
   if ((rc = ensure_device(&num_sms)) != B200MOE_OK) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 
-  // The output starts as zeros: GEMM2's epilogue adds every packed row into its token's row, and a token that no
-  // local expert took stays exactly 0.
-  CUDA_TRY(cudaMemset2DAsync(out_bf16, (size_t)out_row_stride * 2, 0, (size_t)hidden * 2, (size_t)T, st));
+  // (the gather kernel also zeroes the output rows, which GEMM2's epilogue adds into)
   CUDA_TRY(launch_permute(ws, topk_ids, ids_row_stride, topk_w, w_row_stride, hidden_states, hidden_row_stride,
                           hidden_scale, scale_stride_t, scale_stride_kb, T, e_local, local_expert_offset, hidden,
-                          kTileM, num_sms, st, placed, segs));
+                          kTileM, num_sms, st, placed, segs, out_bf16, out_row_stride));
 
   // Up to 16 tokens: swapped-operand decode kernels (B200MOE_DECODE=0 turns them off; B200MOE_DECODE=64
   // extends them to 64 tokens, where the 128-row tiles currently measure faster).  Their per-warp scale
@@ -358,7 +365,11 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
   g1.hidden = hidden;
   g1.act = ws.at<__half>(ws.L.act);
   g1.row_amax = ws.at<unsigned>(ws.L.row_amax);
+  g1.tile_done = ws.at<int>(ws.L.tile_done);
+  g1.act_q_out = ws.at<uint8_t>(ws.L.act_q);
+  g1.row_scale_out = ws.at<float>(ws.L.row_scale);
   g1.status = ws.at<int>(ws.L.status);
+  g1.status_mirror = g_status_mirror;
   g1.splitk_scratch = ws.at<float>(ws.L.splitk_scratch);
   g1.splitk_count = ws.at<int>(ws.L.splitk_count);
   // B200MOE_PROF=1: CTA 0 adds cycle counters into the padding after `meta`
@@ -375,7 +386,9 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
     if (stop) CUDA_TRY(cudaEventRecord(stop, st));
   }
 
-  CUDA_TRY(launch_requant(ws, inter, num_sms, st));
+  // decode sizes requantise inside GEMM1 (the CTA that stores an expert's last weight slab); the 128-row tiles
+  // need a pass of their own (see gemm.cu)
+  if (!nt) CUDA_TRY(launch_requant(ws, inter, num_sms, st));
 
   GemmParams g2;
   memset(&g2, 0, sizeof(g2));
@@ -401,6 +414,7 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
   g2.out = reinterpret_cast<__nv_bfloat16*>(out_bf16);
   g2.out_stride = out_row_stride;
   g2.status = g1.status;
+  g2.status_mirror = g1.status_mirror;
   g2.splitk_scratch = g1.splitk_scratch;
   g2.splitk_count = g1.splitk_count + kSplitKSlots;
   g2.prof = prof_on ? ws.at<unsigned long long>(ws.L.meta + 136) : nullptr;
@@ -449,7 +463,7 @@ int b200moe_run(const void* logits, int logits_dtype, const void* bias, int bias
     int num_sms = 0;
     if ((rc = ensure_device(&num_sms)) != B200MOE_OK) return rc;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    if ((rc = clear_counters(ws, e_local, st)) != B200MOE_OK) return rc;
+    // (no memset: this kernel clears the call's counters itself)
     CUDA_TRY(launch_route_place_small(ws, logits, logits_dtype, bias, bias_dtype, T, routed_scaling_factor,
                                       local_expert_offset, e_local, kTileM, st));
     return experts_impl(ids, kTopK, w, kTopK, hidden_states, hidden_row_stride, hidden_scale, scale_stride_t,

@@ -29,7 +29,14 @@ route_place_small_kernel(Workspace ws, const void* __restrict__ logits, int logi
   __shared__ int s_rows;
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  chain_release();   // launched in plain stream order itself (it follows a memset)
+  chain_release();   // launched in plain stream order itself (the first kernel of a call)
+  // The call's counters (status word, meta, split-K and slab arrival counts): cleared here instead of by a
+  // memset of its own, one launch boundary less.  Nothing of them is read before the barriers below.
+  {
+    uint32_t* z = ws.at<uint32_t>(ws.L.status);
+    const int n = (int)((ws.L.chunk_counts - ws.L.status) / 4);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) z[i] = 0u;
+  }
 
   int32_t* topk_ids = ws.at<int32_t>(ws.L.topk_ids);
   float* topk_w = ws.at<float>(ws.L.topk_w);

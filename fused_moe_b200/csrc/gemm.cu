@@ -18,9 +18,12 @@
 //                The block scales are arbitrary (signed) fp32 numbers, so they cannot ride on the
 //                MMA.  (Sixteen warps with 64 columns each fit only 112 registers per thread and
 //                measured slower.)
-// What shaped the hand-offs: an mbarrier wait costs ~180 cycles of latency even when the phase
-// is already complete, a single thread needs ~360 cycles to issue a K block's MMAs and commits,
-// and the promotion warps are the busiest role.  Therefore
+// What shaped the hand-offs (measured with one-off probes on this GPU): an mbarrier wait costs ~180
+// cycles of latency even when the phase is already complete; a single thread needs ~360 cycles to
+// issue a K block's four MMAs and commits, two threads taking turns reach the MMA rate (513 cycles
+// per 128x256x128 block) with the TMA copies running; the promotion warps' read-back plus FMAs take
+// ~500-600 cycles per K block whatever is done about the waits, and a K block's MMAs complete
+// ~700 cycles after their issue ends (390 in isolation).  Therefore
 //   * a promotion warp looks at the NEXT K block's "accumulator written" barrier (non-blocking) before
 //     the last FMAs of the current one, so the look's latency hides under the FMAs;
 //   * "accumulator read back" is a shared-memory counter the promotion warps add to and the
@@ -455,6 +458,12 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, kTmemCols);
+  if (threadIdx.x == 0 && abort_flag[0] && p.status_mirror) {
+    // a wait of this CTA ran out: let the host see the status word without a copy of its own
+    p.status_mirror[1] = p.status[kStatusDetail];
+    p.status_mirror[0] = p.status[kStatusCode];
+    __threadfence_system();
+  }
 }
 
 template <int MODE>

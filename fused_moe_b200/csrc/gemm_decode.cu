@@ -88,9 +88,11 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
   const uint32_t bar_xready = bar_drain + 16;    // 2 barriers: u of an up warp is in shared memory
   const uint32_t bar_xfree = bar_xready + 16;    // 2 barriers: its gate warp has read it
   const uint32_t bar_split = bar_xfree + 16;     // 2 barriers (split K): partial sums written; arrival order known
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 2 * kRing + 8);
+  const uint32_t bar_rq = bar_split + 16;        // 2 barriers (GEMM1): this item's activations stored; verdict known
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 2 * kRing + 10);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* split_flag = reinterpret_cast<volatile int*>(tmem_slot + 3);
+  volatile int* rq_flag = reinterpret_cast<volatile int*>(tmem_slot + 4);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -112,6 +114,8 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
     }
     mbar_init(bar_split, 4);
     mbar_init(bar_split + 8, 1);
+    mbar_init(bar_rq, 4);
+    mbar_init(bar_rq + 8, 1);
     abort_flag[0] = 0;
     abort_flag[1] = 0;
     fence_mbar_init();
@@ -225,7 +229,7 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
   } else if (warp >= 4 && warp < 8) {
     // ------------------------------ promotion + epilogue ------------------------------
     const int q = warp & 3;                 // TMEM lane quarter: weight rows 32q .. 32q+31 of the slab
-    uint32_t it = 0, xi = 0, si = 0;
+    uint32_t it = 0, xi = 0, si = 0, ri = 0;
     bool alive = true;
     long long ew_wait = 0;
     const long long ebegin = PROF ? clock64() : 0;
@@ -373,6 +377,55 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
           if (lane == 0) mbar_arrive(bar_xfree + 8 * pr);
         }
         ++xi;
+        if (p.tile_done) {
+          // Requantisation inside this kernel: an expert's 32 weight slabs count their arrivals, and the CTA
+          // that stores the last one finds all of the expert's (at most NT) activation rows and their
+          // final maxima in L2 and turns them into e4m3 codes with one scale per row (max|act| / 448,
+          // solution/python/moe_fused.cu:175-195 of the reference).  A CTA runs one or two items at these
+          // sizes, so the round trip of the counting atomic is paid once or twice.
+          const uint32_t rph = ri & 1u;
+          ++ri;
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_rq);            // this warp's stores and row maxima are issued
+          if (warp == 4) {
+            bool okr = mbar_wait(bar_rq, rph, abort_flag, p.status, 31);
+            okr = __all_sync(0xffffffffu, okr);
+            if (!okr) { alive = false; break; }
+            if (lane == 0) {
+              __threadfence();   // the four warps' stores (ordered before this point by the barrier) before the count
+              const int prev = atomicAdd(p.tile_done + m_tile, 1);
+              *rq_flag = prev == p.n_tiles - 1 ? 1 : 0;
+              mbar_arrive(bar_rq + 8);
+            }
+          }
+          bool okq = mbar_wait(bar_rq + 8, rph, abort_flag, p.status, 32);
+          okq = __all_sync(0xffffffffu, okq);
+          if (!okq) { alive = false; break; }
+          if (*rq_flag) {
+            __threadfence();
+            const int tid = (warp - 4) * 32 + lane;
+            const int vecs = p.inter / 8;              // 8 halves = 16 bytes in, 8 bytes out
+            for (int j = 0; j < cnt; ++j) {
+              const int m = row0 + j;
+              const float amax = fmaxf(__uint_as_float(__ldcg(p.row_amax + m)), 1e-8f);
+              const float sc = fmaxf(amax / 448.0f, 1e-8f);
+              if (tid == 0) p.row_scale_out[m] = sc;
+              const uint4* src = reinterpret_cast<const uint4*>(p.act + (size_t)m * p.inter);
+              uint2* dstq = reinterpret_cast<uint2*>(p.act_q_out + (size_t)m * p.inter);
+              for (int v = tid; v < vecs; v += 128) {
+                const uint4 raw = __ldcg(src + v);
+                const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+                const float2 b2 = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+                const float2 c = __half22float2(*reinterpret_cast<const __half2*>(&raw.z));
+                const float2 d = __half22float2(*reinterpret_cast<const __half2*>(&raw.w));
+                uint2 pk;
+                pk.x = pack4_e4m3(a.x / sc, a.y / sc, b2.x / sc, b2.y / sc);
+                pk.y = pack4_e4m3(c.x / sc, c.y / sc, d.x / sc, d.y / sc);
+                dstq[v] = pk;
+              }
+            }
+          }
+        }
       } else {
         const int col = slab * kSlabRows + q * 32 + lane;    // output column of this lane
 #pragma unroll
@@ -393,6 +446,12 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+  if (threadIdx.x == 0 && abort_flag[0] && p.status_mirror) {
+    // a wait of this CTA ran out: let the host see the status word without a copy of its own
+    p.status_mirror[1] = p.status[kStatusDetail];
+    p.status_mirror[0] = p.status[kStatusCode];
+    __threadfence_system();
+  }
 }
 
 template <int MODE, int NT>

@@ -37,7 +37,7 @@ cudaError_t launch_permute(const Workspace& ws, const int32_t* ids, long long id
                            long long w_stride, const uint8_t* hidden, long long hidden_row_stride,
                            const float* hscale, long long sstride_t, long long sstride_kb, int T, int e_local,
                            int local_off, int hidden_dim, int pad_rows, int num_sms, cudaStream_t stream,
-                           bool placed = false, const RowSegments* segs = nullptr);
+                           bool placed, const RowSegments* segs, void* out_bf16, long long out_row_stride);
 
 // Routing + scan + placement of at most kFrontSmallMaxTokens tokens in one block (front_small.cu);
 // writes the workspace's own topk_ids / topk_w.
@@ -70,11 +70,15 @@ struct GemmParams {
   int hidden;
   __half* act;              // GEMM1 out: [m_cap][inter] fp16
   unsigned* row_amax;       // GEMM1 out: bits of max |act| per row
+  int* tile_done;           // decode GEMM1: slabs of each expert tile whose activations are stored (zero at call start)
+  uint8_t* act_q_out;       // decode GEMM1 out (the CTA that stores an expert's last slab): [m_cap][inter] e4m3
+  float* row_scale_out;     // decode GEMM1 out (same CTA): requantisation scale per row
   const float* row_scale;   // GEMM2 in: requantisation scale per row
   const float* row_weight;  // GEMM2 in: routing weight per row
   __nv_bfloat16* out;       // GEMM2 out: the layer's output rows [T][out_stride], zeroed at call start; every packed
   long long out_stride;     //            row is added into its token's row (bf16 red.global.add)
   int* status;
+  int* status_mirror;       // optional host-mapped int32[4]: receives the status word when a CTA gives up on a wait
   float* splitk_scratch;    // decode GEMMs: [kSplitKSlots][kSplitKMax][16][128] partial sums
   int* splitk_count;        // decode GEMMs: arrivals per weight slab, zero at kernel start and end
   unsigned long long* prof;   // optional cycle counters of CTA 0 (null: off)

@@ -133,11 +133,22 @@ place_kernel(Workspace ws, const int32_t* __restrict__ ids, long long ids_stride
 __global__ void __launch_bounds__(256)
 gather_kernel(Workspace ws, const uint8_t* __restrict__ hidden, long long hidden_row_stride,
               const float* __restrict__ hscale, long long sstride_t, long long sstride_kb, int hidden_dim,
-              RowSegments segs) {
+              RowSegments segs, __nv_bfloat16* __restrict__ out, long long out_stride, int T) {
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   chain_wait();
   chain_release();
+  // The layer's output starts as zeros: GEMM2's epilogue adds every packed row into its token's row, and a
+  // token that no local expert took stays exactly 0.  Zeroed here, by all blocks, instead of by a memset
+  // of its own (one launch boundary less; this kernel runs before the GEMMs in every call).
+  {
+    const int vec_per_row = hidden_dim / 8;   // 8 bf16 = 16 bytes
+    const long long total = (long long)T * vec_per_row;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+      const long long t = i / vec_per_row;
+      reinterpret_cast<uint4*>(out + t * out_stride)[i - t * vec_per_row] = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
   const int rows = ws.at<int>(ws.L.meta)[1];
   const int* row_token = ws.at<int>(ws.L.row_token);
   uint8_t* a_packed = ws.at<uint8_t>(ws.L.a_packed);
@@ -174,7 +185,7 @@ cudaError_t launch_permute(const Workspace& ws, const int32_t* ids, long long id
                            long long w_stride, const uint8_t* hidden, long long hidden_row_stride,
                            const float* hscale, long long sstride_t, long long sstride_kb, int T, int e_local,
                            int local_off, int hidden_dim, int pad_rows, int num_sms, cudaStream_t stream,
-                           bool placed, const RowSegments* segs) {
+                           bool placed, const RowSegments* segs, void* out_bf16, long long out_row_stride) {
   const int n_chunks = (T + kChunkTokens - 1) / kChunkTokens;
   cudaError_t err = cudaSuccess;
   if (!placed) {
@@ -195,7 +206,8 @@ cudaError_t launch_permute(const Workspace& ws, const int32_t* ids, long long id
     RowSegments none;
     none.n = 0;
     err = launch_chained(gather_kernel, dim3(blocks), dim3(256), 0, stream, ws, hidden, hidden_row_stride, hscale,
-                         sstride_t, sstride_kb, hidden_dim, segs ? *segs : none);
+                         sstride_t, sstride_kb, hidden_dim, segs ? *segs : none,
+                         reinterpret_cast<__nv_bfloat16*>(out_bf16), out_row_stride, T);
   }
   return err;
 }

@@ -17,9 +17,9 @@ Differences a caller can observe, all documented at the boundary:
   (what the reference does, kernel.py:613-635) and, for callers that bring fresh tensors every
   call, one graph per SHAPE that reads the token inputs from staging buffers, so new tensors cost
   three small device copies instead of a re-capture;
-* the device status word of every call is copied to pinned host memory behind the call and looked
-  at when the next call with the same workspace starts: a bounded device wait that ran out raises
-  ``MoEError`` there (``check_status=True`` still synchronises and raises at once).
+* a kernel that gives up on a bounded device wait mirrors the status word into pinned host memory
+  (``b200moe_set_status_mirror``); it is looked at when the next call with the same workspace
+  starts and raises ``MoEError`` there (``check_status=True`` still synchronises and raises at once).
 
 torch is used for tensors, streams and the workspace allocation only; every kernel
 is in ``libb200moe.so``.
@@ -57,9 +57,8 @@ class Workspace:
         self.ptr = (self.buffer.data_ptr() + 255) // 256 * 256
         self._skip = self.ptr - self.buffer.data_ptr()
         self.out = torch.empty((max(T, 1), hidden), dtype=torch.bfloat16, device=device)
-        # status word of the last call, copied behind it without a synchronisation (see post_status)
+        # pinned (device-accessible) mirror of the status word: a kernel that gives up on a bounded wait writes it
         self.status_host = torch.zeros(4, dtype=torch.int32).pin_memory()
-        self._status_dev = self.buffer[self._skip:self._skip + 16].view(torch.int32)   # `status` is at offset 0
 
     def layout_of_last_call(self):
         """Offsets as the library computed them for the last call's token count (they depend
@@ -75,12 +74,12 @@ class Workspace:
         nb = n * torch.empty((), dtype=dtype).element_size()
         return self.buffer[off:off + nb].view(dtype).view(*shape)
 
-    def post_status(self):
-        """Enqueues the copy of the status word to pinned host memory on the current stream."""
-        self.status_host.copy_(self._status_dev, non_blocking=True)
+    def arm_status_mirror(self):
+        """Tells the library where this thread's next calls mirror a device-side failure."""
+        _capi.lib().b200moe_set_status_mirror(self.status_host.data_ptr())
 
     def raise_if_failed(self):
-        """Looks at the last status word that has reached the host (no synchronisation)."""
+        """Looks at the mirror (no synchronisation): non-zero once a kernel of an earlier call gave up."""
         code = int(self.status_host[0])
         if code != 0:
             detail = self.status_host.tolist()
@@ -252,6 +251,7 @@ def custom_kernel(routing_logits, routing_bias, hidden_states, hidden_states_sca
         lt, bt = _dtype_tag(logits, "routing_logits"), _dtype_tag(bias, "routing_bias")
 
         ws.raise_if_failed()
+        ws.arm_status_mirror()
 
         def launch(lg=logits, bs=bias, h=hs, sc=hidden_states_scale, sc_t=st_t, sc_kb=st_kb, dst=result):
             rc = _capi.lib().b200moe_run(
@@ -262,7 +262,6 @@ def custom_kernel(routing_logits, routing_bias, hidden_states, hidden_states_sca
                 ws.ptr, ws.nbytes, dst.data_ptr(), dst.stride(0),
                 torch.cuda.current_stream(dev).cuda_stream)
             _capi.check(rc, "b200moe_run")
-            ws.post_status()
 
         if T <= GRAPH_MAX_TOKENS and _graphs_enabled() and not torch.cuda.is_current_stream_capturing():
             # Small batches are launch-bound: the launches of a call are replayed as one CUDA graph.

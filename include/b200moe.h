@@ -64,6 +64,7 @@ typedef struct b200moe_ws_layout {
   uint64_t status;        /* int32[16]: [0] status code, [1] detail, [2..] debug */
   uint64_t meta;          /* int32[8]: [0] m_tiles, [1] padded rows, [2] rows with a local expert, [3] pad granularity */
   uint64_t splitk_count;  /* int32[2][64]: arrivals per (GEMM, weight slab) when a decode GEMM splits K; cleared per call */
+  uint64_t tile_done;     /* int32[max_tiles]: decode GEMM1, weight slabs of each expert tile already stored; cleared per call */
   uint64_t chunk_counts;  /* int32[n_chunks][e_local] */
   uint64_t chunk_base;    /* int32[n_chunks][e_local] */
   uint64_t expert_count;  /* int32[e_local] */
@@ -178,6 +179,16 @@ B200MOE_API int b200moe_run(const void* logits, int logits_dtype, const void* bi
 /* Synchronises `stream` and reads the workspace status word: returns B200MOE_OK or the
  * code a kernel recorded; `detail` (host, may be NULL) receives int32[4] of context. */
 B200MOE_API int b200moe_read_status(const void* workspace, void* stream, int32_t* detail /* host */);
+
+/* Asynchronous failure reporting (the reference's calls cannot fail on the device: it has no
+ * device-side waits, solution/python/kernel.py:575-639 checks nothing after its launches): the
+ * calling thread's following b200moe_run / b200moe_experts* calls hand `host_mapped_int4` to their
+ * GEMM kernels, and a CTA that gives up on a bounded wait copies the status word (code, detail)
+ * there besides recording it in the workspace.  The pointer must be device-accessible host memory
+ * (pinned, on a unified-addressing system) of at least four int32 and stay valid while such calls
+ * are in flight; NULL switches the mirror off.  The host looks at it whenever it likes, no copy or
+ * synchronisation per call. */
+B200MOE_API int b200moe_set_status_mirror(void* host_mapped_int4);
 
 /* Measurement hook (no counterpart in the reference, whose per-stage timing replays the
  * pipeline stage by stage from Python, experiments/fast_bench/bench_server.py:470-632):
