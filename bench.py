@@ -51,6 +51,35 @@ UNIT = "tokens/s"
 NCU_TRAFFIC = {"per_row": 14858.0, "per_expert": 31.04e6}   # profiles/grouped_gemm_slice8192_zipf2048.md
 
 
+def bind_to_gpu_numa_node(local_rank: int):
+    """Runs this process on the CPUs of the NUMA node its GPU hangs off, BEFORE any pinned buffer is
+    allocated (pages are placed on the node of the thread that first touches them): with eight ranks
+    copying ~90 MB per step each, buffers that all sit on node 0 send half of the traffic across the
+    socket link.  Returns the node, or None where the topology cannot be read."""
+    try:
+        bus = torch.cuda.get_device_properties(local_rank).pci_bus_id
+        dom = torch.cuda.get_device_properties(local_rank).pci_domain_id
+        dev_id = torch.cuda.get_device_properties(local_rank).pci_device_id
+        path = f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{dev_id:02x}.0/numa_node"
+        with open(path) as fh:
+            node = int(fh.read().strip())
+        if node < 0:
+            return None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as fh:
+            cpus = set()
+            for part in fh.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0)
+        use = cpus & allowed
+        if use:
+            os.sched_setaffinity(0, use)
+            return node
+    except (OSError, ValueError, AttributeError):
+        pass
+    return None
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.isfile(path):
@@ -218,6 +247,7 @@ def run_b200_arm(args):
             raise SystemExit("launch with torch.distributed.run for --gpus > 1")
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    numa_node = bind_to_gpu_numa_node(local_rank) if world > 1 else None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
@@ -269,10 +299,13 @@ def run_b200_arm(args):
     t_wall1 = time.time()
     ms_total = ev0.elapsed_time(ev1)
 
-    if ep is not None and os.environ.get("B200MOE_EP_TRACE"):   # phase breakdown of one step, every rank, to stderr
+    phases = None
+    if ep is not None:   # phase breakdown of one extra step (CUDA events at the phase boundaries), every rank
+        ep._trace = True
         out = step(logits, hq, hsc)
-        print(f"[rank {rank}] ep phases ms: " + json.dumps({k: round(v, 3) for k, v in ep.phase_ms().items()}) +
-              f" recv_rows {ep.last_recv_rows}", file=sys.stderr, flush=True)
+        phases = {k: round(v, 3) for k, v in ep.phase_ms().items()}
+        ep._trace = False
+        ep._marks = []
         barrier()
 
     # GEMM1 in place (separate short loop so that event creation stays out of the headline region)
@@ -302,13 +335,16 @@ def run_b200_arm(args):
     for e in ev_done + ev_out:
         e.record(cur)
 
-    def e2e_step(i):
+    def upload(i):
         k = i & 1
         s_in.wait_event(ev_done[k])                 # the kernels that read this input slot are done
         with torch.cuda.stream(s_in):
             for d, h in zip(d_in[k], host):
                 d.copy_(h, non_blocking=True)
             ev_in[k].record(s_in)
+
+    def compute_and_download(i):
+        k = i & 1
         cur.wait_event(ev_in[k])
         cur.wait_event(ev_out[k])                   # the download that read this output slot is done
         if ep is not None:
@@ -323,12 +359,17 @@ def run_b200_arm(args):
             out_host[k].copy_(o, non_blocking=True)
             ev_out[k].record(s_out)
 
+    # Step i+1's upload is enqueued BEFORE step i's layer call: the expert-parallel call reads the row counts
+    # on the host in its middle, and an upload enqueued behind it would start that much later.
+    upload(0)
     for i in range(4):
-        e2e_step(i)
+        upload(i + 1)
+        compute_and_download(i)
     barrier()
     t0 = time.perf_counter()
-    for i in range(args.steps):
-        e2e_step(i)
+    for i in range(4, 4 + args.steps):
+        upload(i + 1)
+        compute_and_download(i)
     barrier()
     e2e_s = time.perf_counter() - t0
     # clock samples from the start of the device-timed region to the end of the end-to-end loop
@@ -338,10 +379,13 @@ def run_b200_arm(args):
 
     times = torch.tensor([ms_total, e2e_s * 1000.0, g1_avg_ms, float(m_local), float(n_active)],
                          dtype=torch.float64, device=dev)
+    all_phases = None
     if world > 1:
         gathered = [torch.zeros_like(times) for _ in range(world)]
         dist.all_gather(gathered, times)
         allt = torch.stack(gathered).cpu().numpy()
+        all_phases = [None] * world
+        dist.all_gather_object(all_phases, {"rank": rank, "numa_node": numa_node, "phases_ms": phases})
     else:
         allt = times.cpu().numpy()[None]
     ms_total_max = float(allt[:, 0].max())
@@ -396,6 +440,7 @@ def run_b200_arm(args):
         "gpu_launches": launches_per_step * args.steps,
         "roofline": roof, "clocks": clocks,
         "rows_per_rank": [int(x) for x in allt[:, 3]],
+        "ep_phases": all_phases,
         "ep_exchange": (ep.last_mode if ep is not None else None),
     }
 

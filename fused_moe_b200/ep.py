@@ -22,8 +22,8 @@ let the gather read payload and scales from the senders' buffers" (``b200moe_ep_
 they were produced (``b200moe_ep_combine_peers``): plain loads over NVLink, no multicast.  The
 two small NCCL all-to-alls that remain (row counts and offsets before, segment starts after the
 experts) are also what orders the ranks' kernels.  ``B200MOE_EP_P2P=0``, a ``gloo`` group or a
-failed mapping fall back to the NCCL path above.  Both forms give bit-identical outputs
-(tests/test_gpu_ep.py, 2, 4 and 8 GPUs).
+failed mapping fall back to the NCCL path above.  Both forms sum the same partial rows in the
+same order (tests/test_gpu_ep.py, 2, 4 and 8 GPUs).
 
 The exchange logic is independent of the device: tests drive it over ``gloo`` with CPU
 stand-ins for the five device operations (``ops``), the product always uses ``CudaOps``.

@@ -173,8 +173,9 @@ def _nccl_worker(rank, world, port, tokens, ret, p2p):
 
 
 def _both_forms_worker(rank, world, port, tokens, ret):
-    """Both exchange forms in one process group: the outputs must be bit-identical (same partial rows,
-    summed in the same order)."""
+    """Both exchange forms in one process group: the same partial rows summed in the same order.  A partial
+    row itself is the sum of a token's bf16 expert rows in the order GEMM2's tiles finish, so two runs agree
+    up to a few bf16 steps, not bit for bit."""
     import torch.distributed as dist
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
@@ -197,14 +198,20 @@ def _both_forms_worker(rank, world, port, tokens, ret):
             outs.append(out.clone())
             modes.append(ep.last_mode)
             dist.barrier()
-        ret[rank] = (modes, bool(torch.equal(outs[0].view(torch.int16), outs[1].view(torch.int16))),
-                     outs[0].cpu().view(torch.int16).numpy().copy())
+        a32, b32 = outs[0].float(), outs[1].float()
+        if a32.numel():
+            bound = 8 * 2.0 ** -8 * torch.clamp(torch.maximum(a32.abs().amax(dim=1, keepdim=True),
+                                                             b32.abs().amax(dim=1, keepdim=True)), min=1.0)
+            same = bool(((a32 - b32).abs() <= bound).all())
+        else:
+            same = True
+        ret[rank] = (modes, same, outs[0].cpu().view(torch.int16).numpy().copy())
     finally:
         dist.destroy_process_group()
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_both_exchange_forms_agree_bit_for_bit_and_match_the_oracle(world):
+def test_both_exchange_forms_agree_and_match_the_oracle(world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
