@@ -497,7 +497,7 @@ def sweep(kernel, synth, dev, bias, weights, peaks, cpu_fn=None):
         torch.cuda.synchronize()
         ws = kernel.get_workspace(dev, T, 32, HIDDEN, INTER)
         meta = ws.view("meta", torch.int32, (8,)).cpu().numpy()
-        counts = ws.view("expert_count", torch.int32, (32,)).cpu().numpy()
+        counts = ws.view("expert_count", torch.int32, (E,)).cpu().numpy()
         m_local, n_active = int(meta[2]), int((counts > 0).sum())
         ts = []
         for _ in range(10):
@@ -547,7 +547,8 @@ def run_profile_case(args):
     from fused_moe_b200 import kernel, synth
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
-    w = synth.make_weights(32, 0, 0, HIDDEN, INTER, device=dev, fast_device_rng=True)
+    E = args.experts
+    w = synth.make_weights(E, 0, 0, HIDDEN, INTER, device=dev, fast_device_rng=True)
     lg, hq, hsc = (t.to(dev) for t in synth.make_tokens(args.tokens, 0, 0))
     bias = synth.make_bias(0, zipf=args.zipf).to(dev)
     for _ in range(args.warmup):
@@ -559,10 +560,10 @@ def run_profile_case(args):
         kernel.custom_kernel(lg, bias, hq, hsc, *w, 0, RSF, check_status=False)
     b.record()
     torch.cuda.synchronize()
-    ws = kernel.get_workspace(dev, args.tokens, 32, HIDDEN, INTER)
+    ws = kernel.get_workspace(dev, args.tokens, E, HIDDEN, INTER)
     code, detail = ws.read_status(0)
     meta = ws.view("meta", torch.int32, (8,)).cpu().numpy()
-    counts = ws.view("expert_count", torch.int32, (32,)).cpu().numpy()
+    counts = ws.view("expert_count", torch.int32, (E,)).cpu().numpy()
     prof = None
     if os.environ.get("B200MOE_PROF"):
         raw = ws.view("meta", torch.int64, (32,)).cpu().numpy()      # meta + its padding, as u64 words
@@ -579,7 +580,7 @@ def run_profile_case(args):
         for name, t in (("gemm1", tr[0]), ("gemm2", tr[1])) if args.tokens > 16 else ():
             base = int(t[8, 0])
             prof[name]["trace_kb8_31"] = [[int(x) - base for x in t[i]] for i in range(8, 32)]
-    print(json.dumps({"profile_case": "slice32", "tokens": args.tokens, "zipf": args.zipf, "status": code,
+    print(json.dumps({"profile_case": f"slice{E}", "tokens": args.tokens, "zipf": args.zipf, "status": code,
                       "cycle_counters_cta0": prof,
                       "ms_per_call": a.elapsed_time(b) / max(args.steps, 1), "rows": int(meta[2]),
                       "padded_rows": int(meta[1]), "active_experts": int((counts > 0).sum())}), flush=True)
@@ -600,6 +601,8 @@ def main():
                     help="small single-GPU slice case for ncu (see run_profile_case); not a benchmark")
     ap.add_argument("--tokens", type=int, default=8192, help="tokens of --profile-case")
     ap.add_argument("--zipf", action="store_true", help="Zipf routing bias for --profile-case")
+    ap.add_argument("--experts", type=int, default=32, choices=[32, 64, 128, 256],
+                    help="local experts of --profile-case (experts [0, E) of the 256)")
     args = ap.parse_args()
     if args.profile_case:
         run_profile_case(args)

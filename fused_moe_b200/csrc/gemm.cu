@@ -70,8 +70,11 @@ constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kStages = 4;
 constexpr int kRing = 8;                    // activation-scale slots; see the reuse argument at the producer
 constexpr int kRingBytes = kRing * kTileM * 4;
-constexpr int kPanelFloats = 128;           // per promotion warp: two runs of up to 64 weight scales
-constexpr int kPanelBytes = kPromoWarps * kPanelFloats * 4;
+// Per promotion warp and work item, staged one item ahead (two buffers): two runs of up to 64 weight
+// scales, then per lane the row's token, requantisation scale and routing weight.
+constexpr int kPanelFloats = 128;
+constexpr int kItemFloats = kPanelFloats + 3 * 32;
+constexpr int kPanelBytes = kPromoWarps * 2 * kItemFloats * 4;
 constexpr int kMaxKBlocks = 64;
 constexpr int kBarBytes = 256;
 constexpr int kSmemBytes = kStages * kStageBytes + kRingBytes + kPanelBytes + kBarBytes + 1024;   // + alignment slack
@@ -115,6 +118,17 @@ __device__ __forceinline__ void st_smem_f32(uint32_t addr, float v) {
   asm volatile("st.shared::cta.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
+// 4-byte asynchronous copy global -> shared (no register holds the value while it is in flight)
+__device__ __forceinline__ void copy4_async(uint32_t smem_dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copy_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ uint32_t ld_smem_u32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared::cta.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+
 // Bounded poll of a monotonic shared-memory counter (wrap-safe comparison).
 __device__ __forceinline__ bool counter_wait(uint32_t addr, uint32_t target, volatile int* abort_flag, int* status,
                                              int where) {
@@ -147,7 +161,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t ring_base = smem_base + S * kStageBytes;          // [kRing][128] activation scales
-  const uint32_t panel_base = ring_base + kRingBytes;              // [16 warps][128] weight scales
+  const uint32_t panel_base = ring_base + kRingBytes;              // [8 warps][2 buffers][kItemFloats] staged per-item values
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * kStageBytes + kRingBytes + kPanelBytes);
   const uint32_t bar_full = smem_u32(bars);              // S barriers: stage filled by TMA
   const uint32_t bar_empty = bar_full + 8 * S;           // S barriers: stage consumed by the MMAs
@@ -294,7 +308,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     // chunk c < HC sits at col_lo + 32 c, chunk c >= HC at col_hi + 32 (c - HC)
     const uint32_t col_lo = MODE == 1 ? cg * (HC * 32) : cg * (CH * 32);
     const uint32_t col_hi = MODE == 1 ? kBN / 2 + cg * (HC * 32) : cg * (CH * 32) + HC * 32;
-    const uint32_t panel = panel_base + pw * (kPanelFloats * 4);
+    const uint32_t stage_me = panel_base + pw * (2 * kItemFloats * 4);
     const uint32_t ring_me = ring_base + (q * 32 + lane) * 4;
     uint32_t it = 0;
     bool alive = true;
@@ -303,48 +317,51 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
     long long t_wait = 0, t_promote = 0, t_epi = 0;
     const int nblk_per_expert = p.n_per_expert / kBlockK;
     uint32_t peek = 0;   // "accumulator written" of the coming K block already seen complete
-    for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x) {
+    // What an item needs besides its operands - the weight scales of its (expert, N tile) and, per row, the
+    // token and the two output factors - is copied into shared memory while the item BEFORE it is in its K
+    // loop: fetched at the item's start, the chain tile_expert -> scales (two dependent loads under the weight
+    // stream) cost ~5000 cycles per item during which the MMAs ran dry.
+    auto stage_item = [&](int w, int e, uint32_t dst) {
       const int m_tile = w / p.n_tiles, n_tile = w % p.n_tiles;
-      const int e = p.tile_expert[m_tile];
-      const int row = m_tile * kTileM + q * 32 + lane;
-      const int tok = p.row_token[row];
-      // GEMM2: the row's output factors, fetched now so that the epilogue does not wait for them
-      float rs_a = 0.f, rs_b = 0.f;
-      if (MODE == 2 && tok >= 0) {
-        rs_a = p.row_scale[row];
-        rs_b = p.row_weight[row];
+      const float* run0;
+      const float* run1;
+      if (MODE == 1) {
+        run0 = p.b_scale + ((size_t)e * nblk_per_expert + n_tile) * kblocks;                       // gate block
+        run1 = p.b_scale + ((size_t)e * nblk_per_expert + p.inter / kBlockK + n_tile) * kblocks;   // up block
+      } else {
+        run0 = p.b_scale + ((size_t)e * nblk_per_expert + 2 * n_tile + (cg * (CH * 32)) / kBlockK) * kblocks;
+        run1 = run0;
       }
+      if (lane < kblocks) {
+        copy4_async(dst + lane * 4, run0 + lane);
+        if (MODE == 1) copy4_async(dst + (64 + lane) * 4, run1 + lane);
+      }
+      if (lane + 32 < kblocks) {
+        copy4_async(dst + (32 + lane) * 4, run0 + lane + 32);
+        if (MODE == 1) copy4_async(dst + (96 + lane) * 4, run1 + lane + 32);
+      }
+      const int row = m_tile * kTileM + q * 32 + lane;
+      copy4_async(dst + (kPanelFloats + lane) * 4, p.row_token + row);
+      if (MODE == 2) {
+        copy4_async(dst + (kPanelFloats + 32 + lane) * 4, p.row_scale + row);
+        copy4_async(dst + (kPanelFloats + 64 + lane) * 4, p.row_weight + row);
+      }
+    };
+    const int kb_stage = kblocks > 4 ? kblocks - 4 : 0;   // the K block during which the next item is staged
+    uint32_t pb = 0;
+    if ((int)blockIdx.x < total_items) stage_item(blockIdx.x, p.tile_expert[blockIdx.x / p.n_tiles], stage_me);
+    for (int w = blockIdx.x; w < total_items && alive; w += gridDim.x, pb ^= 1u) {
+      const int m_tile = w / p.n_tiles, n_tile = w % p.n_tiles;
+      const int row = m_tile * kTileM + q * 32 + lane;
+      const uint32_t panel = stage_me + pb * (kItemFloats * 4);
+      const int w_next = w + gridDim.x;
+      // read now, used at K block kb_stage: the expert of the next item
+      const int e_next = w_next < total_items ? p.tile_expert[w_next / p.n_tiles] : 0;
       float2 acc[CH * 16];
 #pragma unroll
       for (int j = 0; j < CH * 16; ++j) acc[j] = make_float2(0.f, 0.f);
-
-      // weight scales of this item into the warp's panel: run 0 at [0, 64), run 1 at [64, 128)
-      {
-        const float* run0;
-        const float* run1;
-        if (MODE == 1) {
-          run0 = p.b_scale + ((size_t)e * nblk_per_expert + n_tile) * kblocks;                       // gate block
-          run1 = p.b_scale + ((size_t)e * nblk_per_expert + p.inter / kBlockK + n_tile) * kblocks;   // up block
-        } else {
-          run0 = p.b_scale + ((size_t)e * nblk_per_expert + 2 * n_tile + (cg * (CH * 32)) / kBlockK) * kblocks;
-          run1 = run0;
-        }
-        float v0 = 0.f, v1 = 0.f, v2 = 0.f, v3 = 0.f;
-        if (lane < kblocks) v0 = run0[lane];
-        if (lane + 32 < kblocks) v1 = run0[lane + 32];
-        if (MODE == 1) {
-          if (lane < kblocks) v2 = run1[lane];
-          if (lane + 32 < kblocks) v3 = run1[lane + 32];
-        }
-        __syncwarp();   // every lane is done reading the previous item's panel
-        st_smem_f32(panel + lane * 4, v0);
-        st_smem_f32(panel + (lane + 32) * 4, v1);
-        if (MODE == 1) {
-          st_smem_f32(panel + (64 + lane) * 4, v2);
-          st_smem_f32(panel + (96 + lane) * 4, v3);
-        }
-        __syncwarp();
-      }
+      copy_async_wait_all();   // this item's staged values (copied during the previous item's K loop)
+      __syncwarp();
 
       for (int kb = 0; kb < kblocks; ++kb, ++it) {
         const uint32_t b = it & 1u, bph = (it >> 1) & 1u;
@@ -393,6 +410,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           fma_chunk(acc + 48, rb, sc1);
         }
         peek = __all_sync(0xffffffffu, pk != 0u) ? 1u : 0u;
+        if (kb == kb_stage && w_next < total_items) stage_item(w_next, e_next, stage_me + (pb ^ 1u) * (kItemFloats * 4));
         if (PROF) {
           const long long c2 = clock64();
           t_wait += c1 - c0;
@@ -402,6 +420,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       if (!alive) break;
       const long long te0 = PROF ? clock64() : 0;
 
+      const int tok = (int)ld_smem_u32(panel + (kPanelFloats + lane) * 4);
       if (tok >= 0) {
         if (MODE == 1) {
           // acc[0 .. HC*16) = gate columns (pairs), acc[HC*16 ..) = the matching up columns.
@@ -429,8 +448,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
           // token's output row (zeroed at call start), eight bf16 sums per 16-byte red.global.add - the
           // arithmetic of the reference's `out[t] += bf16(G2 * w)` on a bf16 tensor
           // (experiments/fast_bench/correctness_bench.py:107-111), in the order the tiles finish
-          asm volatile("" : "+f"(rs_a), "+f"(rs_b));   // keeps the product (and the wait for the two loads) down here
-          const float rs = rs_a * rs_b;
+          const float rs = ld_smem_f32(panel + (kPanelFloats + 32 + lane) * 4) * ld_smem_f32(panel + (kPanelFloats + 64 + lane) * 4);
           __nv_bfloat16* dst = p.out + (size_t)tok * p.out_stride + n_tile * kBN + cg * (CH * 32);
 #pragma unroll
           for (int j = 0; j < CH * 16; j += 4) {
@@ -446,6 +464,7 @@ grouped_gemm_kernel(const __grid_constant__ GemmParams p) {
       }
       if (PROF) t_epi += clock64() - te0;
     }
+    copy_async_wait_all();   // (an aborted item loop may leave copies of the next item's values in flight)
     if (prof_me) {
       p.prof[0] = (unsigned long long)t_wait;                  // waiting for an accumulator
       p.prof[1] = (unsigned long long)t_promote;               // TMEM read-back + FMAs
