@@ -497,7 +497,7 @@ def sweep(kernel, synth, dev, bias, weights, peaks, cpu_fn=None):
         torch.cuda.synchronize()
         ws = kernel.get_workspace(dev, T, 32, HIDDEN, INTER)
         meta = ws.view("meta", torch.int32, (8,)).cpu().numpy()
-        counts = ws.view("expert_count", torch.int32, (E,)).cpu().numpy()
+        counts = ws.view("expert_count", torch.int32, (32,)).cpu().numpy()
         m_local, n_active = int(meta[2]), int((counts > 0).sum())
         ts = []
         for _ in range(10):

@@ -127,6 +127,23 @@ int make_tmap_gate_up(CUtensorMap* map, const void* base, uint64_t e_local, uint
 
 uint64_t align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
 
+// Decode-size calls (up to 16 tokens) take the swapped-operand kernels (B200MOE_DECODE=0 turns them off;
+// B200MOE_DECODE=64 extends them to 64 tokens, where the 128-row tiles currently measure faster).  Their
+// per-warp scale panels hold a bounded number of K blocks; larger shapes take the grouped kernels.
+// Returns the token tile of the decode kernels, or 0 for the grouped kernels.
+int decode_tile(int T, int hidden, int inter) {
+  static const bool decode_on = [] {
+    const char* v = getenv("B200MOE_DECODE");
+    return !(v && v[0] == '0');
+  }();
+  static const int decode_max_t = [] {
+    const char* v = getenv("B200MOE_DECODE");
+    return (v && v[0] == '6') ? 64 : 16;
+  }();
+  const bool fits = hidden / kBlockK <= decode_gemm_max_kblocks() && inter / kBlockK <= decode_gemm_max_kblocks();
+  return (decode_on && fits && T <= decode_max_t) ? (T <= 16 ? 16 : 64) : 0;
+}
+
 int shape_ok(int T, int e_local, int hidden, int inter) {
   if (T < 0 || e_local < 1) return B200MOE_ERR_INVALID_ARGUMENT;
   if (e_local > kNumExperts || hidden < 256 || hidden % 256 != 0 || inter < 128 || inter % 128 != 0)
@@ -328,19 +345,7 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
                           hidden_scale, scale_stride_t, scale_stride_kb, T, e_local, local_expert_offset, hidden,
                           kTileM, num_sms, st, placed, segs, out_bf16, out_row_stride));
 
-  // Up to 16 tokens: swapped-operand decode kernels (B200MOE_DECODE=0 turns them off; B200MOE_DECODE=64
-  // extends them to 64 tokens, where the 128-row tiles currently measure faster).  Their per-warp scale
-  // panels hold a bounded number of K blocks; larger shapes take the 128-row tiles.
-  static const bool decode_on = [] {
-    const char* v = getenv("B200MOE_DECODE");
-    return !(v && v[0] == '0');
-  }();
-  static const int decode_max_t = [] {
-    const char* v = getenv("B200MOE_DECODE");
-    return (v && v[0] == '6') ? 64 : 16;
-  }();
-  const bool decode_fits = hidden / kBlockK <= decode_gemm_max_kblocks() && inter / kBlockK <= decode_gemm_max_kblocks();
-  const int nt = (decode_on && decode_fits && T <= decode_max_t) ? (T <= 16 ? 16 : 64) : 0;
+  const int nt = decode_tile(T, hidden, inter);
 
   GemmParams g1;
   memset(&g1, 0, sizeof(g1));

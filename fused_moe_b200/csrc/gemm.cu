@@ -28,8 +28,24 @@
 //     the last FMAs of the current one, so the look's latency hides under the FMAs;
 //   * "accumulator read back" is a shared-memory counter the promotion warps add to and the
 //     issuer polls with plain acquire loads (~30 cycles) instead of a second mbarrier;
-//   * activation scales arrive in shared memory with the operands (same barrier), weight scales
-//     of an item sit in a per-warp panel, so the K loop touches no global memory.
+//   * activation scales arrive in shared memory with the operands (same barrier); the weight scales of an
+//     item and its rows' token / output factors are copied into a per-warp panel while the item BEFORE it
+//     is in its K loop (cp.async), so neither the K loop nor an item's start waits on global memory.
+// Also measured, and slower or no faster (cycles per 128x256x128 K block, this kernel: ~940):
+//   * handing the accumulator over in two 128-column halves (N = 128 MMAs, four barriers): ~1000 - an
+//     N = 128 MMA of one CTA takes ~90 cycles instead of 64 (it re-reads A from shared memory twice as often,
+//     and shared memory is already ~80 % busy with TMA writes and operand reads), so the tensor pipe alone
+//     needs ~720;
+//   * rings of their own for the two operands (three A slots, five B slots): no faster, and with rings of odd
+//     length the two issuing threads alternate on a slot, so a parity wait can take the phase before last
+//     for the current one - each issuer then has to publish which K blocks it has seen landed;
+//   * CTA pairs on 256 x 128 tiles with four 128-column accumulators, a thread's 64 columns read in one go
+//     and the next K block's read-back in flight during the FMAs: ~1000 per half-sized step - a step has
+//     the same four or five dependent shared-memory round trips (~110 cycles each under this load) as a K
+//     block here, for half of the FMAs;
+//   * zeros instead of stale bytes in the padding rows of an expert's last tile, and a bare hand-off loop for
+//     promotion warps whose 32 rows are all padding: no change of the step time under the board's power limit
+//     (a sustained run settles near 1.5-1.6 GHz), and the extra loop cost the main one ~4 %.
 // GEMM1 pairs gate rows [n, n+128) with up rows [inter+n, ...) in one tile, so the epilogue
 // computes g*silu(u) in registers, stores fp16 activations and the row maximum.  (Requantising
 // inside this kernel - the CTA that completes the last N tile of an M tile turning the tile's rows
@@ -113,9 +129,6 @@ __device__ __forceinline__ float ld_smem_f32(uint32_t addr) {
   float v;
   asm volatile("ld.shared::cta.f32 %0, [%1];" : "=f"(v) : "r"(addr) : "memory");
   return v;
-}
-__device__ __forceinline__ void st_smem_f32(uint32_t addr, float v) {
-  asm volatile("st.shared::cta.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
 
 // 4-byte asynchronous copy global -> shared (no register holds the value while it is in flight)
