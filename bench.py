@@ -276,7 +276,7 @@ def run_b200_arm(args):
     for _ in range(max(args.warmup, 3)):
         out = step(logits, hq, hsc)
     barrier()
-    ws = kernel.get_workspace(dev, ep.last_recv_rows if ep else TOKENS_PER_RANK, e_local, HIDDEN, INTER)
+    ws = kernel.get_workspace(dev, ep.last_ws_rows if ep else TOKENS_PER_RANK, e_local, HIDDEN, INTER)
     code, detail = ws.read_status(torch.cuda.current_stream().cuda_stream)
     if code != 0:
         raise SystemExit(f"device status {code} {detail} after warm-up")

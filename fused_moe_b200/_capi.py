@@ -34,7 +34,8 @@ class WsLayout(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in (
         "total_bytes", "status", "meta", "splitk_count", "tile_done", "chunk_counts", "chunk_base", "expert_count",
         "expert_row0", "tile_expert", "row_token", "row_weight", "a_packed", "a_scale", "act",
-        "row_amax", "act_q", "row_scale", "tok_rows", "topk_ids", "topk_w", "trace", "splitk_scratch")] + [
+        "row_amax", "act_q", "row_scale", "tok_rows", "topk_ids", "topk_w", "trace", "splitk_scratch",
+        "ep_segments")] + [
         (n, C.c_int32) for n in ("m_cap", "max_tiles", "n_chunks", "chunk_tokens")]
 
 
@@ -61,8 +62,7 @@ SIGNATURES = {
     "b200moe_launches_per_run": (_I, [_I, _I]),
     "b200moe_ep_pack": (_I, [_P, _P, _P, _L, _P, _L, _L, _I, _I, _I, _P, _P, _P, _P]),
     "b200moe_ep_combine": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),
-    "b200moe_ep_pull_ids": (_I, [_P, _P, _I, _L, _I, _P, _P, _P]),
-    "b200moe_experts_segments": (_I, [_P, _P, _P, _P, _I, _L, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _P, _L, _P]),
+    "b200moe_ep_local_experts": (_I, [_P, _P, _I, _I, _L, _P, _P, _P, _P, _I, _I, _I, _I, _P, _Z, _P, _L, _P]),
     "b200moe_ep_combine_peers": (_I, [_P, _P, _P, _I, _I, _I, _P, _P]),
 }
 

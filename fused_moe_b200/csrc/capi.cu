@@ -189,6 +189,7 @@ void compute_layout(int T, int e_local, int hidden, int inter, b200moe_ws_layout
   L->topk_w = take((uint64_t)(T > 0 ? T : 1) * kTopK * 4);
   L->trace = take(2 * 8 * 64 * 8);   // B200MOE_PROF: absolute cycle stamps of CTA 0's first 64 K blocks
   L->splitk_scratch = take((uint64_t)kSplitKSlots * kSplitKMax * 16 * 128 * 4);   // 2 MiB
+  L->ep_segments = take(256);   // RowSegments at +0, int32 row count at +192 (b200moe_ep_local_experts)
   L->total_bytes = off;
 }
 
@@ -313,15 +314,17 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
                         int64_t scale_stride_t, int64_t scale_stride_kb, const uint8_t* w1, const float* w1_scale,
                         const uint8_t* w2, const float* w2_scale, int T, int e_local, int local_expert_offset,
                         int hidden, int inter, void* workspace, size_t workspace_bytes, void* out_bf16,
-                        int64_t out_row_stride, void* stream, bool placed, const RowSegments* segs = nullptr) {
+                        int64_t out_row_stride, void* stream, bool placed, const RowSegments* segs = nullptr,
+                        const RowSegments* segs_dev = nullptr, const int* n_rows_dev = nullptr) {
   // The event pair armed by b200moe_profile_next_gemm1 is for this call only: forget it on every
   // way out (the GEMM1 launch below consumes it first when the call gets that far).
   struct DisarmProfile {
     ~DisarmProfile() { g_prof_start = g_prof_stop = nullptr; }
   } disarm_profile;
   if (!topk_ids || !topk_w || !w1 || !w1_scale || !w2 || !w2_scale) return B200MOE_ERR_INVALID_ARGUMENT;
-  if (T > 0 && ((!segs && (!hidden_states || !hidden_scale)) || !out_bf16)) return B200MOE_ERR_INVALID_ARGUMENT;
-  if (segs) {   // rows are read from the segments: no separate payload / scale arrays
+  if (T > 0 && ((!segs && !segs_dev && (!hidden_states || !hidden_scale)) || !out_bf16))
+    return B200MOE_ERR_INVALID_ARGUMENT;
+  if (segs || segs_dev) {   // rows are read from the segments: no separate payload / scale arrays
     hidden_row_stride = hidden;
     hidden_states = nullptr;
   }
@@ -343,7 +346,7 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
   // (the gather kernel also zeroes the output rows, which GEMM2's epilogue adds into)
   CUDA_TRY(launch_permute(ws, topk_ids, ids_row_stride, topk_w, w_row_stride, hidden_states, hidden_row_stride,
                           hidden_scale, scale_stride_t, scale_stride_kb, T, e_local, local_expert_offset, hidden,
-                          kTileM, num_sms, st, placed, segs, out_bf16, out_row_stride));
+                          kTileM, num_sms, st, placed, segs, out_bf16, out_row_stride, segs_dev, n_rows_dev));
 
   const int nt = decode_tile(T, hidden, inter);
 
@@ -522,54 +525,42 @@ int b200moe_ep_pack(const int32_t* topk_ids, const float* topk_w, const uint8_t*
   return B200MOE_OK;
 }
 
-namespace {
-int fill_segments(const void* const* seg_base, const int32_t* seg_rows, int n_segs, int64_t row_bytes, int hidden,
-                  RowSegments* segs, int* total_rows) {
-  if (!seg_base || !seg_rows || n_segs < 1 || n_segs > 8) return B200MOE_ERR_INVALID_ARGUMENT;
+int b200moe_ep_local_experts(const void* const* send_base, const int32_t* from_peers, int world, int cap_rows,
+                             int64_t row_bytes, const uint8_t* w1, const float* w1_scale, const uint8_t* w2,
+                             const float* w2_scale, int e_local, int local_expert_offset, int hidden, int inter,
+                             void* workspace, size_t workspace_bytes, void* out_bf16, int64_t out_row_stride,
+                             void* stream) {
+  if (!send_base || !from_peers || cap_rows < 0) return B200MOE_ERR_INVALID_ARGUMENT;
+  if (world != 1 && world != 2 && world != 4 && world != 8) return B200MOE_ERR_UNSUPPORTED_SHAPE;
   if (row_bytes < hidden + 4 * (hidden / kBlockK) + 64 || row_bytes % 16 != 0) return B200MOE_ERR_MISALIGNED;
-  memset(segs, 0, sizeof(*segs));
-  segs->n = n_segs;
-  segs->row_bytes = row_bytes;
-  int run = 0;
-  for (int s = 0; s < n_segs; ++s) {
-    if (seg_rows[s] < 0 || (seg_rows[s] > 0 && !seg_base[s])) return B200MOE_ERR_INVALID_ARGUMENT;
-    if (reinterpret_cast<uintptr_t>(seg_base[s]) % 16 != 0) return B200MOE_ERR_MISALIGNED;
-    segs->start[s] = run;
-    segs->base[s] = reinterpret_cast<const uint8_t*>(seg_base[s]);
-    run += seg_rows[s];
+  if (local_expert_offset < 0 || local_expert_offset + e_local > kNumExperts) return B200MOE_ERR_INVALID_ARGUMENT;
+  PeerBases bases;
+  memset(&bases, 0, sizeof(bases));
+  for (int s = 0; s < world; ++s) {
+    if (!send_base[s]) return B200MOE_ERR_INVALID_ARGUMENT;
+    if (reinterpret_cast<uintptr_t>(send_base[s]) % 16 != 0) return B200MOE_ERR_MISALIGNED;
+    bases.base[s] = reinterpret_cast<const uint8_t*>(send_base[s]);
   }
-  for (int s = n_segs; s < 9; ++s) segs->start[s] = run;
-  *total_rows = run;
-  return B200MOE_OK;
-}
-}  // namespace
-
-int b200moe_ep_pull_ids(const void* const* seg_base, const int32_t* seg_rows, int n_segs, int64_t row_bytes,
-                        int hidden, int32_t* topk_ids, float* topk_w, void* stream) {
-  RowSegments segs;
-  int rows = 0;
-  int rc = fill_segments(seg_base, seg_rows, n_segs, row_bytes, hidden, &segs, &rows);
+  Workspace ws;
+  int rc = bind_workspace(cap_rows, e_local, hidden, inter, workspace, workspace_bytes, &ws);
   if (rc != B200MOE_OK) return rc;
-  if (rows == 0) return B200MOE_OK;
-  if (!topk_ids || !topk_w) return B200MOE_ERR_INVALID_ARGUMENT;
+  if (cap_rows == 0) return B200MOE_OK;
   int num_sms = 0;
   if ((rc = ensure_device(&num_sms)) != B200MOE_OK) return rc;
-  CUDA_TRY(launch_ep_pull_ids(segs, rows, hidden, topk_ids, topk_w, num_sms, reinterpret_cast<cudaStream_t>(stream)));
-  return B200MOE_OK;
-}
-
-int b200moe_experts_segments(const int32_t* topk_ids, const float* topk_w, const void* const* seg_base,
-                             const int32_t* seg_rows, int n_segs, int64_t row_bytes, const uint8_t* w1,
-                             const float* w1_scale, const uint8_t* w2, const float* w2_scale, int e_local,
-                             int local_expert_offset, int hidden, int inter, void* workspace, size_t workspace_bytes,
-                             void* out_bf16, int64_t out_row_stride, void* stream) {
-  RowSegments segs;
-  int rows = 0;
-  int rc = fill_segments(seg_base, seg_rows, n_segs, row_bytes, hidden, &segs, &rows);
-  if (rc != B200MOE_OK) return rc;
-  return experts_impl(topk_ids, kTopK, topk_w, kTopK, nullptr, hidden, nullptr, 0, 0, w1, w1_scale, w2, w2_scale, rows,
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if ((rc = clear_counters(ws, e_local, st)) != B200MOE_OK) return rc;
+  RowSegments* segs_dev = ws.at<RowSegments>(ws.L.ep_segments);
+  int* n_rows_dev = ws.at<int>(ws.L.ep_segments + 192);
+  static_assert(sizeof(RowSegments) <= 192, "the segment table and the row count share 256 bytes");
+  int32_t* ids = ws.at<int32_t>(ws.L.topk_ids);
+  float* w = ws.at<float>(ws.L.topk_w);
+  CUDA_TRY(launch_ep_segments_pull(bases, from_peers, world, row_bytes, cap_rows, hidden, segs_dev, n_rows_dev, ids, w,
+                                   num_sms, st));
+  CUDA_TRY(launch_count(ids, kTopK, cap_rows, local_expert_offset, e_local, ws.at<int>(ws.L.chunk_counts), num_sms, st,
+                        n_rows_dev));
+  return experts_impl(ids, kTopK, w, kTopK, nullptr, hidden, nullptr, 0, 0, w1, w1_scale, w2, w2_scale, cap_rows,
                       e_local, local_expert_offset, hidden, inter, workspace, workspace_bytes, out_bf16, out_row_stride,
-                      stream, false, &segs);
+                      stream, false, nullptr, segs_dev, n_rows_dev);
 }
 
 int b200moe_ep_combine_peers(const void* const* partial_bf16, const int32_t* row_start, const int32_t* send_slot,

@@ -149,10 +149,39 @@ ep_combine_kernel(const __nv_bfloat16* __restrict__ returned, const int32_t* __r
   }
 }
 
+// Builds the segment table of this step from the (count, offset) pairs the sources sent (one thread).
+__global__ void ep_segments_kernel(PeerBases send_base, const int32_t* __restrict__ from_peers, int n,
+                                   long long row_bytes, int cap_rows, RowSegments* __restrict__ segs_out,
+                                   int* __restrict__ n_rows_out) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  RowSegments sg;
+  sg.n = n;
+  sg.row_bytes = row_bytes;
+  int run = 0;
+  for (int s = 0; s < 8; ++s) {
+    int cnt = 0, off = 0;
+    if (s < n) {
+      cnt = from_peers[3 * s];
+      off = from_peers[3 * s + 1];
+      if (cnt < 0) cnt = 0;
+      if (cnt > cap_rows - run) cnt = cap_rows - run;   // never past the capacity the workspace was sized for
+    }
+    sg.start[s] = run;
+    sg.base[s] = s < n ? send_base.base[s] + (size_t)off * row_bytes : nullptr;
+    run += cnt;
+  }
+  sg.start[8] = run;
+  for (int s = n; s < 8; ++s) sg.start[s] = run;
+  *segs_out = sg;
+  *n_rows_out = run;
+}
+
 // ids + weights of every send row addressed to this rank, read where the sender packed them
 __global__ void __launch_bounds__(256)
-ep_pull_ids_kernel(RowSegments segs, int rows, int hidden_dim, int32_t* __restrict__ ids_out,
-                   float* __restrict__ w_out) {
+ep_pull_ids_kernel(const RowSegments* __restrict__ segs_dev, const int* __restrict__ n_rows_dev, int hidden_dim,
+                   int32_t* __restrict__ ids_out, float* __restrict__ w_out) {
+  const RowSegments segs = *segs_dev;
+  const int rows = *n_rows_dev;
   const int trailer = hidden_dim + 4 * (hidden_dim / kBlockK);   // byte offset of ids[8] | weights[8]
   const long long n = (long long)rows * 16;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
@@ -204,14 +233,17 @@ ep_combine_peers_kernel(PeerPartials peers, const int32_t* __restrict__ row_star
 
 }  // namespace
 
-cudaError_t launch_ep_pull_ids(const RowSegments& segs, int rows, int hidden_dim, int32_t* ids_out, float* w_out,
-                               int num_sms, cudaStream_t stream) {
-  if (rows <= 0) return cudaSuccess;
-  long long n = (long long)rows * 16;
-  int blocks = (int)((n + 255) / 256);
+cudaError_t launch_ep_segments_pull(const PeerBases& send_base, const int32_t* from_peers, int n, long long row_bytes,
+                                    int cap_rows, int hidden_dim, RowSegments* segs_out, int* n_rows_out,
+                                    int32_t* ids_out, float* w_out, int num_sms, cudaStream_t stream) {
+  ep_segments_kernel<<<1, 32, 0, stream>>>(send_base, from_peers, n, row_bytes, cap_rows, segs_out, n_rows_out);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess || cap_rows <= 0) return err;
+  long long work = (long long)cap_rows * 16;
+  int blocks = (int)((work + 255) / 256);
   int cap = num_sms * 8;
   if (blocks > cap) blocks = cap;
-  ep_pull_ids_kernel<<<blocks, 256, 0, stream>>>(segs, rows, hidden_dim, ids_out, w_out);
+  ep_pull_ids_kernel<<<blocks, 256, 0, stream>>>(segs_out, n_rows_out, hidden_dim, ids_out, w_out);
   return cudaGetLastError();
 }
 

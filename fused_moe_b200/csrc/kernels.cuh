@@ -11,8 +11,10 @@ cudaError_t launch_route(const void* logits, int logits_dtype, const void* bias,
                          int local_off, int e_local, int32_t* ids, float* w, int* chunk_counts, int num_sms,
                          cudaStream_t stream);
 
+// `n_rows_dev` (optional, device): the number of rows actually present, when the host only knows the
+// capacity T (expert-parallel calls whose row counts never leave the device).
 cudaError_t launch_count(const int32_t* ids, long long row_stride, int T, int local_off, int e_local,
-                         int* chunk_counts, int num_sms, cudaStream_t stream);
+                         int* chunk_counts, int num_sms, cudaStream_t stream, const int* n_rows_dev = nullptr);
 
 // Rows that live in up to eight separate buffers (the send buffers of the ranks of an
 // expert-parallel group, this GPU's own or its peers' mapped memory): row r of the virtual
@@ -37,7 +39,8 @@ cudaError_t launch_permute(const Workspace& ws, const int32_t* ids, long long id
                            long long w_stride, const uint8_t* hidden, long long hidden_row_stride,
                            const float* hscale, long long sstride_t, long long sstride_kb, int T, int e_local,
                            int local_off, int hidden_dim, int pad_rows, int num_sms, cudaStream_t stream,
-                           bool placed, const RowSegments* segs, void* out_bf16, long long out_row_stride);
+                           bool placed, const RowSegments* segs, void* out_bf16, long long out_row_stride,
+                           const RowSegments* segs_dev = nullptr, const int* n_rows_dev = nullptr);
 
 // Routing + scan + placement of at most kFrontSmallMaxTokens tokens in one block (front_small.cu);
 // writes the workspace's own topk_ids / topk_w.
@@ -105,8 +108,16 @@ cudaError_t launch_ep_pack(const int32_t* ids, const float* w, const uint8_t* hi
                            int world, uint8_t* send_rows, int32_t* dest_counts, int32_t* send_slot, int num_sms,
                            cudaStream_t stream);
 // ids + weights (the 64-byte trailer) of every row of `segs` into compact local arrays [rows][8]
-cudaError_t launch_ep_pull_ids(const RowSegments& segs, int rows, int hidden_dim, int32_t* ids_out, float* w_out,
-                               int num_sms, cudaStream_t stream);
+// The segment table of an expert-parallel step built ON THE DEVICE from what the small all-to-all delivered:
+// `from_peers` [n][3] int32 = (rows source s has for this rank, their first row in s's send buffer, unused),
+// `send_base[s]` = source s's (mapped) send buffer.  Writes the table and the total row count (clamped to
+// `cap_rows`) to `segs_out` / `n_rows_out`, then copies the (ids, weights) trailer of every row.
+struct PeerBases {
+  const uint8_t* base[8];
+};
+cudaError_t launch_ep_segments_pull(const PeerBases& send_base, const int32_t* from_peers, int n, long long row_bytes,
+                                    int cap_rows, int hidden_dim, RowSegments* segs_out, int* n_rows_out,
+                                    int32_t* ids_out, float* w_out, int num_sms, cudaStream_t stream);
 // ep_combine reading each destination's partial rows where they were produced: partial[d] is rank d's
 // (mapped) output buffer, row_start[d] (device) the first row of this rank's segment inside it
 struct PeerPartials {

@@ -82,10 +82,12 @@ scan_kernel(Workspace ws, int e_local, int n_chunks, int pad_rows) {
 
 __global__ void __launch_bounds__(1024)
 place_kernel(Workspace ws, const int32_t* __restrict__ ids, long long ids_stride,
-             const float* __restrict__ w, long long w_stride, int T, int local_off, int e_local) {
+             const float* __restrict__ w, long long w_stride, int T, int local_off, int e_local,
+             const int* __restrict__ n_rows_dev) {
   __shared__ int s_ids[kTopK][kChunkTokens];   // [k][token]: conflict-free when lanes walk tokens
   chain_wait();
   chain_release();
+  if (n_rows_dev) T = min(T, *n_rows_dev);   // T was the capacity; rows past the count hold nothing
   const int c = blockIdx.x;
   const int t0 = c * kChunkTokens;
   for (int i = threadIdx.x; i < kChunkTokens * kTopK; i += blockDim.x) {
@@ -133,11 +135,14 @@ place_kernel(Workspace ws, const int32_t* __restrict__ ids, long long ids_stride
 __global__ void __launch_bounds__(256)
 gather_kernel(Workspace ws, const uint8_t* __restrict__ hidden, long long hidden_row_stride,
               const float* __restrict__ hscale, long long sstride_t, long long sstride_kb, int hidden_dim,
-              RowSegments segs, __nv_bfloat16* __restrict__ out, long long out_stride, int T) {
+              RowSegments segs, __nv_bfloat16* __restrict__ out, long long out_stride, int T,
+              const RowSegments* __restrict__ segs_dev, const int* __restrict__ n_rows_dev) {
   const int lane = threadIdx.x & 31;
   const int warps_per_block = blockDim.x >> 5;
   chain_wait();
   chain_release();
+  if (segs_dev) segs = *segs_dev;            // the table was built on the device (see launch_ep_segments_pull)
+  if (n_rows_dev) T = min(T, *n_rows_dev);
   // The layer's output starts as zeros: GEMM2's epilogue adds every packed row into its token's row, and a
   // token that no local expert took stays exactly 0.  Zeroed here, by all blocks, instead of by a memset
   // of its own (one launch boundary less; this kernel runs before the GEMMs in every call).
@@ -185,7 +190,8 @@ cudaError_t launch_permute(const Workspace& ws, const int32_t* ids, long long id
                            long long w_stride, const uint8_t* hidden, long long hidden_row_stride,
                            const float* hscale, long long sstride_t, long long sstride_kb, int T, int e_local,
                            int local_off, int hidden_dim, int pad_rows, int num_sms, cudaStream_t stream,
-                           bool placed, const RowSegments* segs, void* out_bf16, long long out_row_stride) {
+                           bool placed, const RowSegments* segs, void* out_bf16, long long out_row_stride,
+                           const RowSegments* segs_dev, const int* n_rows_dev) {
   const int n_chunks = (T + kChunkTokens - 1) / kChunkTokens;
   cudaError_t err = cudaSuccess;
   if (!placed) {
@@ -196,7 +202,7 @@ cudaError_t launch_permute(const Workspace& ws, const int32_t* ids, long long id
     if (!placed) {
       // 32 warps per chunk: a call has few chunks, and a warp's walk over its experts is a chain of small loads
       err = launch_chained(place_kernel, dim3(n_chunks), dim3(1024), 0, stream, ws, ids, ids_stride, w, w_stride, T,
-                           local_off, e_local);
+                           local_off, e_local, n_rows_dev);
       if (err != cudaSuccess) return err;
     }
     long long cap_rows = ws.L.m_cap;
@@ -207,7 +213,7 @@ cudaError_t launch_permute(const Workspace& ws, const int32_t* ids, long long id
     none.n = 0;
     err = launch_chained(gather_kernel, dim3(blocks), dim3(256), 0, stream, ws, hidden, hidden_row_stride, hscale,
                          sstride_t, sstride_kb, hidden_dim, segs ? *segs : none,
-                         reinterpret_cast<__nv_bfloat16*>(out_bf16), out_row_stride, T);
+                         reinterpret_cast<__nv_bfloat16*>(out_bf16), out_row_stride, T, segs_dev, n_rows_dev);
   }
   return err;
 }

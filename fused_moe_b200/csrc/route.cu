@@ -42,8 +42,9 @@ route_kernel(const void* __restrict__ logits, int logits_dtype, const void* __re
 
 __global__ void __launch_bounds__(256)
 count_kernel(const int32_t* __restrict__ ids, long long row_stride, int T, int local_off, int e_local,
-             int* __restrict__ chunk_counts) {
+             int* __restrict__ chunk_counts, const int* __restrict__ n_rows_dev) {
   chain_release();
+  if (n_rows_dev) T = min(T, *n_rows_dev);
   long long n = (long long)T * kTopK;
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     int t = (int)(i / kTopK), k = (int)(i % kTopK);
@@ -67,13 +68,13 @@ cudaError_t launch_route(const void* logits, int logits_dtype, const void* bias,
 }
 
 cudaError_t launch_count(const int32_t* ids, long long row_stride, int T, int local_off, int e_local,
-                         int* chunk_counts, int num_sms, cudaStream_t stream) {
+                         int* chunk_counts, int num_sms, cudaStream_t stream, const int* n_rows_dev) {
   if (T <= 0) return cudaSuccess;
   long long n = (long long)T * kTopK;
   int blocks = (int)((n + 255) / 256);
   int cap = num_sms * 8;
   if (blocks > cap) blocks = cap;
-  count_kernel<<<blocks, 256, 0, stream>>>(ids, row_stride, T, local_off, e_local, chunk_counts);
+  count_kernel<<<blocks, 256, 0, stream>>>(ids, row_stride, T, local_off, e_local, chunk_counts, n_rows_dev);
   return cudaGetLastError();
 }
 

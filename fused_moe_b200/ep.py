@@ -16,13 +16,14 @@ exchanges around it.  Per call, on every rank:
 
 With NCCL ranks on one node the two bulk exchanges are folded into the kernels instead
 (``PeerExchange``): the send buffer and the partial-output buffer of every rank are
-symmetric-memory allocations mapped into every process, steps 4-5 become "pull the ids, then
-let the gather read payload and scales from the senders' buffers" (``b200moe_ep_pull_ids``,
-``b200moe_experts_segments``) and steps 6-7 become one kernel that sums the partial rows where
-they were produced (``b200moe_ep_combine_peers``): plain loads over NVLink, no multicast.  The
-two small NCCL all-to-alls that remain (row counts and offsets before, segment starts after the
-experts) are also what orders the ranks' kernels.  ``B200MOE_EP_P2P=0``, a ``gloo`` group or a
-failed mapping fall back to the NCCL path above.  Both forms sum the same partial rows in the
+symmetric-memory allocations mapped into every process, steps 3-5 become "exchange (count,
+offset) pairs, build the segment table ON THE DEVICE, pull the ids and let the gather read
+payload and scales from the senders' buffers" (``b200moe_ep_local_experts``: the host never
+reads a count, the workspace is sized for the exchange's capacity) and steps 6-7 become one
+kernel that sums the partial rows where they were produced (``b200moe_ep_combine_peers``):
+plain loads over NVLink, no multicast.  The two small NCCL all-to-alls that remain (row counts
+and offsets before, segment starts after the experts) are also what orders the ranks' kernels.
+``B200MOE_EP_P2P=0``, a ``gloo`` group or a failed mapping fall back to the NCCL path above.  Both forms sum the same partial rows in the
 same order (tests/test_gpu_ep.py, 2, 4 and 8 GPUs).
 
 The exchange logic is independent of the device: tests drive it over ``gloo`` with CPU
@@ -182,8 +183,13 @@ class ExpertParallelMoE:
         self.e_local = E_GLOBAL // self.world
         self.local_off = self.rank * self.e_local
         self.ops = ops if ops is not None else CudaOps()
-        self.last_recv_rows = 0
+        self._last_recv_rows = 0
+        self.last_ws_rows = 0          # the token count the workspace of the last local expert pipeline was laid out for
         self.last_send_counts: List[int] = []
+        self._exch_host = None         # pinned copy of what the last peer-memory step exchanged
+        self._exch_event = None
+        self._exch_pending = False
+        self._misfit_dev = None
         # B200MOE_EP_TRACE=1: CUDA events at the phase boundaries of every forward; phase_ms() reads them
         self._trace = bool(os.environ.get("B200MOE_EP_TRACE")) and isinstance(self.ops, CudaOps)
         self._marks: list = []
@@ -213,8 +219,10 @@ class ExpertParallelMoE:
                 self._peer, self._peer_failed = None, True
                 return None
         # A batch that does not fit this rank's mapped buffers is NOT refused here: the other ranks could not
-        # know and would block in the next collective.  _forward_peer sends every rank's token count along
-        # with the row counts, and all ranks raise together (see exchange_counts).
+        # know and would block in the next collective.  _forward_peer sends a "fits" flag along with the row
+        # counts; the rank itself sends nothing and raises after the step, the others at their next call.
+        if hidden != self._peer.hidden:     # the same on every rank (the model's width): nobody enters a collective
+            raise ValueError(f"hidden size {hidden} differs from the mapped exchange buffers' {self._peer.hidden}")
         return self._peer
 
     def _mark(self, name: str):
@@ -239,6 +247,7 @@ class ExpertParallelMoE:
             raise ValueError(f"rank holds {w1.shape[0]} experts, expected {self.e_local}")
         if world == 1:
             self.last_recv_rows = T
+            self.last_ws_rows = T
             return _k.custom_kernel(routing_logits, routing_bias, hidden_states, hidden_states_scale,
                                     w1, s1, w2, s2, 0, routed_scaling_factor) \
                 if isinstance(ops, CudaOps) else self._single(routing_logits, routing_bias, hidden_states,
@@ -258,15 +267,12 @@ class ExpertParallelMoE:
 
         # counts: what I send to d  <->  what d will receive from me
         self._mark("route_pack")
-        recv_counts = torch.empty_like(dest_counts)
-        dist.all_to_all_single(recv_counts, dest_counts, group=self.group)
-        both = torch.stack([dest_counts, recv_counts]).cpu().tolist()    # one host read for both
+        send_n, recv_n, _, _ = exchange_counts(dest_counts, True, self.group)   # one host read (NCCL needs split sizes)
         self._mark("counts_exchange_and_host_read")
-        send_n = [int(x) for x in both[0]]
-        recv_n = [int(x) for x in both[1]]
         self.last_send_counts = send_n
         n_recv, n_send = sum(recv_n), sum(send_n)
         self.last_recv_rows = n_recv
+        self.last_ws_rows = n_recv
         rb = send_rows.shape[1]
 
         # dispatch: compact per-destination segments out, per-source segments in
@@ -290,9 +296,11 @@ class ExpertParallelMoE:
 
     def _forward_peer(self, peer: PeerExchange, routing_logits, routing_bias, hidden_states, hidden_states_scale,
                       w1, s1, w2, s2, rsf) -> torch.Tensor:
-        """The step with both bulk exchanges folded into the kernels (see the module docstring)."""
+        """The step with both bulk exchanges folded into the kernels (see the module docstring).  Nothing
+        is read back by the host inside the step: what the small all-to-all delivered is copied to pinned
+        memory behind the step and looked at by ``check_exchange`` (start of the next call, or on demand)."""
         import ctypes as C
-        world, ops, me = self.world, self.ops, self.rank
+        world, ops = self.world, self.ops
         T, hidden = hidden_states.shape
         inter = w2.shape[2]
         dev = hidden_states.device
@@ -300,56 +308,49 @@ class ExpertParallelMoE:
         self.last_mode = "peer"
         self._marks = []
         self._mark("start")
-        fits = T <= peer.cap_tokens and hidden == peer.hidden
+        fits = T <= peer.cap_tokens
         if fits:
             ids, w = ops.route(routing_logits, routing_bias, rsf, self.local_off, self.e_local, hidden, inter)
             send_rows, dest_counts, send_slot = ops.pack(ids, w, hidden_states, hidden_states_scale, world,
                                                          send_buffer=peer.send)
-        else:   # nothing of this batch may touch the mapped buffers; the ranks learn of it below
+        else:   # nothing of this batch may touch the mapped buffers: this rank sends nothing and raises below,
+            #     the others learn of it from the flag (they still get a complete, collective step)
             dest_counts = torch.zeros((world,), dtype=torch.int32, device=dev)
+            send_slot = torch.full((max(T, 1), world), -1, dtype=torch.int32, device=dev)
         self._mark("route_pack")
-        # to every destination: how many rows it gets from me and where they start in my send buffer.
-        # This exchange completes only after every rank's pack kernel: it is also what makes the
-        # send buffers safe to read.
-        send_n, recv_n, recv_off, misfits = exchange_counts(dest_counts, fits, self.group)
-        if misfits:
-            raise ValueError(f"rank(s) {misfits} hold a batch that exceeds the mapped exchange buffers "
-                             f"({peer.cap_tokens} tokens of width {peer.hidden}; this rank: {T} x {hidden}); every rank "
-                             f"raises, no collective is left pending; pass max_tokens to ExpertParallelMoE")
-        self.last_send_counts = send_n
-        n_recv = sum(recv_n)
-        self.last_recv_rows = n_recv
-        self._mark("counts_exchange_and_host_read")
+        # Before the first collective of this step: did some rank overrun its buffers in the previous one (then
+        # that rank has raised and may never come here)?  Every other rank raises at this point.  The wait is for
+        # the previous step's small copy; this step's routing and packing are already queued behind it.
+        self.check_exchange()
+        # to every destination: how many rows it gets from me, where they start in my send buffer, and whether
+        # my batch fitted.  This exchange completes only after every rank's pack kernel: it is also what makes
+        # the send buffers safe to read.
+        seg_off = torch.cumsum(dest_counts, 0, dtype=torch.int32) - dest_counts
+        flag = torch.full_like(dest_counts, 0 if fits else 1)
+        mine = torch.stack([dest_counts, seg_off, flag], dim=1).contiguous()    # [world, 3]
+        theirs = torch.empty_like(mine)
+        dist.all_to_all_single(theirs, mine, group=self.group)
+        self._mark("counts_exchange")
 
         rb = peer.row_bytes
-        seg_base = (C.c_void_p * world)(*[peer.send_ptrs[s] + recv_off[s] * rb for s in range(world)])
-        seg_rows = (C.c_int32 * world)(*recv_n)
+        cap_rows = world * peer.cap_tokens
+        bases = (C.c_void_p * world)(*peer.send_ptrs)
         stream = torch.cuda.current_stream(dev).cuda_stream
-        if n_recv > 0:
-            r_ids = torch.empty((n_recv, TOP_K), dtype=torch.int32, device=dev)
-            r_w = torch.empty((n_recv, TOP_K), dtype=torch.float32, device=dev)
-            w1b, w2b = _k._as_bytes(w1, "gemm1_weights"), _k._as_bytes(w2, "gemm2_weights")
-            with torch.cuda.device(dev):
-                ws = _k.get_workspace(dev, n_recv, self.e_local, hidden, inter)
-                ws.last_T = n_recv
-                _capi.check(lib.b200moe_ep_pull_ids(seg_base, seg_rows, world, rb, hidden, r_ids.data_ptr(),
-                                                    r_w.data_ptr(), stream), "b200moe_ep_pull_ids")
-                _capi.check(lib.b200moe_count(r_ids.data_ptr(), TOP_K, n_recv, self.local_off, self.e_local, hidden,
-                                              inter, ws.ptr, ws.nbytes, stream), "b200moe_count")
-                _capi.check(lib.b200moe_experts_segments(
-                    r_ids.data_ptr(), r_w.data_ptr(), seg_base, seg_rows, world, rb,
-                    w1b.data_ptr(), s1.data_ptr(), w2b.data_ptr(), s2.data_ptr(), self.e_local, self.local_off,
-                    hidden, inter, ws.ptr, ws.nbytes, peer.partial.data_ptr(), hidden, stream),
-                    "b200moe_experts_segments")
+        w1b, w2b = _k._as_bytes(w1, "gemm1_weights"), _k._as_bytes(w2, "gemm2_weights")
+        with torch.cuda.device(dev):
+            ws = _k.get_workspace(dev, cap_rows, self.e_local, hidden, inter)
+            ws.last_T = cap_rows
+            _capi.check(lib.b200moe_ep_local_experts(
+                bases, theirs.data_ptr(), world, cap_rows, rb, w1b.data_ptr(), s1.data_ptr(), w2b.data_ptr(),
+                s2.data_ptr(), self.e_local, self.local_off, hidden, inter, ws.ptr, ws.nbytes,
+                peer.partial.data_ptr(), hidden, stream), "b200moe_ep_local_experts")
+        self.last_ws_rows = cap_rows
         self._mark("local_experts_reading_peers")
 
         # to every source: where its segment starts in my partial buffer.  Enqueued after the expert
         # kernels, so its completion on a rank means that every rank's partial rows are written.
-        starts, run = [], 0
-        for n in recv_n:
-            starts.append(run)
-            run += n
-        seg_start = torch.tensor(starts, dtype=torch.int32).to(dev, non_blocking=True)
+        recv = theirs[:, 0].contiguous()
+        seg_start = (torch.cumsum(recv, 0, dtype=torch.int32) - recv).contiguous()
         row_start = torch.empty_like(seg_start)
         dist.all_to_all_single(row_start, seg_start, group=self.group)
         self._mark("segment_starts_exchange")
@@ -359,7 +360,52 @@ class ExpertParallelMoE:
             _capi.check(lib.b200moe_ep_combine_peers(parts, row_start.data_ptr(), send_slot.data_ptr(), T, hidden,
                                                      world, out.data_ptr(), stream), "b200moe_ep_combine_peers")
         self._mark("combine_reading_peers")
+        # what was exchanged, for the host to look at AFTER the step (no wait here); the "did not fit" flags
+        # accumulate on the device, so a step the host never looked at cannot hide one
+        if self._exch_host is None or self._exch_host.shape[1] != world:
+            self._exch_host = torch.zeros((3, world, 3), dtype=torch.int32).pin_memory()
+            self._exch_event = torch.cuda.Event()
+            self._misfit_dev = torch.zeros((world, 3), dtype=torch.int32, device=dev)
+        self._misfit_dev[:, 0].bitwise_or_(theirs[:, 2])
+        self._exch_host[0].copy_(mine, non_blocking=True)
+        self._exch_host[1].copy_(theirs, non_blocking=True)
+        self._exch_host[2].copy_(self._misfit_dev, non_blocking=True)
+        self._exch_event.record(torch.cuda.current_stream(dev))
+        self._exch_pending = True
+        if not fits:
+            raise ValueError(f"this rank's batch ({T} x {hidden}) exceeds the mapped exchange buffers "
+                             f"({peer.cap_tokens} tokens of width {peer.hidden}); it sent nothing, the other ranks "
+                             f"raise at their next call; pass max_tokens to ExpertParallelMoE")
         return out[:T]
+
+    def check_exchange(self, block: bool = True):
+        """Looks at what the last peer-memory step exchanged: updates ``last_send_counts`` /
+        ``last_recv_rows`` and raises when some rank's batch had not fitted its mapped buffers in any step
+        since the last look (every rank sees the same flags, one or more calls later).  ``block=False``
+        looks only if that step's small copy has already landed, so the host keeps running ahead."""
+        if not self._exch_pending:
+            return
+        if not block and not self._exch_event.query():
+            return
+        self._exch_event.synchronize()
+        self._exch_pending = False
+        mine, theirs, flags = (self._exch_host[i].tolist() for i in range(3))
+        self.last_send_counts = [int(r[0]) for r in mine]
+        self._last_recv_rows = sum(int(r[0]) for r in theirs)
+        misfits = [s for s in range(self.world) if int(flags[s][0]) != 0]
+        if misfits:
+            self._misfit_dev.zero_()
+            raise ValueError(f"rank(s) {misfits} held a batch that exceeds the mapped exchange buffers in an "
+                             f"earlier step and sent nothing; pass max_tokens to ExpertParallelMoE")
+
+    @property
+    def last_recv_rows(self) -> int:
+        self.check_exchange()
+        return self._last_recv_rows
+
+    @last_recv_rows.setter
+    def last_recv_rows(self, v: int):
+        self._last_recv_rows = int(v)
 
     def _single(self, logits, bias, hs, hsc, w1, s1, w2, s2, rsf):
         ids, w = self.ops.route(logits, bias, rsf, 0, self.e_local, hs.shape[1], w2.shape[2])

@@ -83,6 +83,7 @@ typedef struct b200moe_ws_layout {
   uint64_t topk_w;        /* float[T][8]  (used by b200moe_run) */
   uint64_t trace;         /* uint64[2][64][8]: cycle stamps written when B200MOE_PROF is set */
   uint64_t splitk_scratch; /* float[64][4][16][128]: partial sums of a decode GEMM whose K range is split over CTAs */
+  uint64_t ep_segments;    /* 256 bytes: segment table and row count of b200moe_ep_local_experts (device-written) */
   int32_t m_cap;          /* capacity in packed rows (multiple of 128) */
   int32_t max_tiles;
   int32_t n_chunks;
@@ -231,29 +232,28 @@ B200MOE_API int b200moe_ep_combine(const void* returned_bf16, const int32_t* sen
 
 /* ---- the same exchange over mapped peer memory (NVLink loads inside the kernels instead of
  * NCCL all-to-all; no counterpart in the reference) ----
- * A "segment" s is the part of rank s's send buffer (b200moe_ep_pack layout) addressed to this
- * rank: seg_base[s] points at its first row (this GPU's own memory or a peer's mapped into this
- * process), seg_rows[s] is its row count; both arrays are HOST arrays of n_segs <= 8 entries.
- * The virtual row order is segment 0, then segment 1, ...  The caller orders the kernels:
- * the senders' pack kernels must have completed (e.g. the counts exchange between the ranks
- * runs after them), and a sender must not repack before the readers are done. */
-
-/* ids and weights (the 64-byte trailer) of every segment row into compact [rows][8] arrays. */
-B200MOE_API int b200moe_ep_pull_ids(const void* const* seg_base, const int32_t* seg_rows, int n_segs,
-                        int64_t row_bytes, int hidden, int32_t* topk_ids, float* topk_w, void* stream);
-
-/* b200moe_experts whose gather reads payload and scales straight from the segments
- * (dispatch and gather in one pass).  topk_ids / topk_w: the compact arrays of
- * b200moe_ep_pull_ids; b200moe_count on them must have run.  out row r belongs to virtual row r. */
-B200MOE_API int b200moe_experts_segments(const int32_t* topk_ids, const float* topk_w,
-                        const void* const* seg_base, const int32_t* seg_rows, int n_segs, int64_t row_bytes,
+ * The local expert pipeline of one expert-parallel step, reading its rows where the ranks packed them
+ * (dispatch and gather in one pass) and with every row count staying on the device.
+ *   send_base   HOST array of `world` pointers: rank s's send buffer (b200moe_ep_pack layout) as mapped
+ *               into this process (this GPU's own memory for s == this rank).
+ *   from_peers  DEVICE int32[world][3], what the small all-to-all between the ranks delivered: row s =
+ *               (rows rank s has for this rank, index of their first row in rank s's send buffer, unused).
+ *   cap_rows    the largest total the ranks can send here (world x the exchange's token capacity); the
+ *               workspace is sized for it: b200moe_workspace_layout(cap_rows, ...).
+ * Builds the segment table on the device (virtual row order: rank 0's rows, then rank 1's, ...), copies
+ * the rows' (ids, weights) trailers, counts, places, gathers and runs both GEMMs; out row r belongs to
+ * virtual row r.  Nothing is read back by the host.  The caller orders the kernels between ranks: the
+ * senders' pack kernels must have completed (the exchange that delivers from_peers runs after them), and
+ * a sender must not repack before the readers are done. */
+B200MOE_API int b200moe_ep_local_experts(const void* const* send_base, const int32_t* from_peers, int world,
+                        int cap_rows, int64_t row_bytes,
                         const uint8_t* w1, const float* w1_scale, const uint8_t* w2, const float* w2_scale,
                         int e_local, int local_expert_offset, int hidden, int inter,
                         void* workspace, size_t workspace_bytes,
                         void* out_bf16, int64_t out_row_stride, void* stream);
 
 /* b200moe_ep_combine with the return exchange folded in: partial_bf16[d] (HOST array of `world`
- * pointers) is rank d's output buffer of b200moe_experts_segments as mapped here, row_start[d]
+ * pointers) is rank d's output buffer of b200moe_ep_local_experts as mapped here, row_start[d]
  * (DEVICE int32[world]) the first row of this rank's segment inside it.  The caller makes sure
  * every rank's expert kernels have completed (e.g. the exchange that delivers row_start runs
  * after them). */

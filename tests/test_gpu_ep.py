@@ -96,31 +96,30 @@ def test_exchange_read_in_place_with_emulated_ranks(world, T):
         torch.cuda.synchronize()
         packed.append((rows, counts.cpu().numpy(), slot))
     partials, starts = [], []          # per expert rank d: its output rows; start of each source's segment in it
+    cap_rows = world * max(max(T), 1)  # what the exchange's buffers could deliver to one rank
     for d in range(world):
         recv_n = [int(packed[s][1][d]) for s in range(world)]
         offs = [int(packed[s][1][:d].sum()) for s in range(world)]
         n_recv = sum(recv_n)
         starts.append([sum(recv_n[:s]) for s in range(world)])
-        seg_base = (C.c_void_p * world)(*[packed[s][0].data_ptr() + offs[s] * rb for s in range(world)])
-        seg_rows = (C.c_int32 * world)(*recv_n)
-        partial = torch.zeros((max(n_recv, 1), HIDDEN), dtype=torch.bfloat16, device=dev)
+        # the whole send buffers and, ON THE DEVICE, (count, first row) per source: what the ranks' small
+        # all-to-all delivers; the library builds the segment table from it without a host read
+        bases = (C.c_void_p * world)(*[packed[s][0].data_ptr() for s in range(world)])
+        from_peers = torch.tensor([[recv_n[s], offs[s], 0] for s in range(world)], dtype=torch.int32, device=dev)
+        partial = torch.zeros((cap_rows, HIDDEN), dtype=torch.bfloat16, device=dev)
+        wd = tuple(t[d * per:(d + 1) * per].to(dev) for t in all_w)
+        w1b, w2b = K._as_bytes(wd[0], "gemm1_weights"), K._as_bytes(wd[2], "gemm2_weights")
+        ws = K.get_workspace(dev, cap_rows, per, HIDDEN, INTER)
+        ws.last_T = cap_rows
+        _capi.check(lib.b200moe_ep_local_experts(
+            bases, from_peers.data_ptr(), world, cap_rows, rb, w1b.data_ptr(), wd[1].data_ptr(), w2b.data_ptr(),
+            wd[3].data_ptr(), per, d * per, HIDDEN, INTER, ws.ptr, ws.nbytes, partial.data_ptr(), HIDDEN, stream),
+            "ep_local_experts")
+        torch.cuda.synchronize()
+        assert ws.read_status(stream)[0] == 0
         if n_recv:
-            r_ids = torch.empty((n_recv, 8), dtype=torch.int32, device=dev)
-            r_w = torch.empty((n_recv, 8), dtype=torch.float32, device=dev)
-            wd = tuple(t[d * per:(d + 1) * per].to(dev) for t in all_w)
-            w1b, w2b = K._as_bytes(wd[0], "gemm1_weights"), K._as_bytes(wd[2], "gemm2_weights")
-            ws = K.get_workspace(dev, n_recv, per, HIDDEN, INTER)
-            ws.last_T = n_recv
-            _capi.check(lib.b200moe_ep_pull_ids(seg_base, seg_rows, world, rb, HIDDEN, r_ids.data_ptr(),
-                                                r_w.data_ptr(), stream), "pull_ids")
-            _capi.check(lib.b200moe_count(r_ids.data_ptr(), 8, n_recv, d * per, per, HIDDEN, INTER, ws.ptr,
-                                          ws.nbytes, stream), "count")
-            _capi.check(lib.b200moe_experts_segments(
-                r_ids.data_ptr(), r_w.data_ptr(), seg_base, seg_rows, world, rb, w1b.data_ptr(),
-                wd[1].data_ptr(), w2b.data_ptr(), wd[3].data_ptr(), per, d * per, HIDDEN, INTER, ws.ptr, ws.nbytes,
-                partial.data_ptr(), HIDDEN, stream), "experts_segments")
-            torch.cuda.synchronize()
             # the pulled ids are the senders' routing results, row for row
+            r_ids = ws.view("topk_ids", torch.int32, (cap_rows, 8))[:n_recv]
             sent = torch.cat([packed[s][0][offs[s]:offs[s] + recv_n[s]] for s in range(world) if recv_n[s]])
             trailer = HIDDEN + 4 * (HIDDEN // 128)
             assert torch.equal(r_ids.cpu(), sent[:, trailer:trailer + 32].contiguous().view(torch.int32).cpu())
@@ -251,3 +250,58 @@ def test_nccl_exchange_on_two_gpus_matches_single_rank_oracle(p2p):
         got = torch.from_numpy(ret[r]).view(torch.bfloat16)
         frac_all, frac_nz, max_abs = synth.check_close(got, ref["out"])
         assert frac_all >= 0.999, (r, frac_all, max_abs)
+
+
+def _overflow_worker(rank, world, port, ret):
+    """Step 0 fits on both ranks; in step 1 rank 1 brings more tokens than the mapped buffers hold.  Rank 1 takes
+    part in that step's collectives with nothing to send and raises after them; rank 0 completes the step (its
+    own tokens only went to experts of both ranks as usual) and raises before the first collective of step 2.
+    Nobody is left waiting in a collective, and no device wait is involved."""
+    import torch.distributed as dist
+    os.environ["B200MOE_EP_P2P"] = "1"
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    dev = torch.device("cuda", rank)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        per = 256 // world
+        w = synth.make_weights(per, rank * per, SEED, HIDDEN, INTER, device=dev)
+        bias = synth.make_bias(SEED).to(dev)
+        small = tuple(t.to(dev) for t in synth.make_tokens(64, rank, SEED, HIDDEN))
+        big = tuple(t.to(dev) for t in synth.make_tokens(200, rank, SEED, HIDDEN))
+        ep = ExpertParallelMoE(max_tokens=128)
+        events = []
+        ep.forward(small[0], bias, small[1], small[2], *w, 2.5)
+        events.append("step0 ok")
+        if ep.last_mode != "peer":
+            ret[rank] = ["no peer memory"]
+            return
+        try:
+            batch = big if rank == 1 else small
+            ep.forward(batch[0], bias, batch[1], batch[2], *w, 2.5)
+            events.append("step1 ok")
+        except ValueError as exc:
+            events.append("step1 raised: " + str(exc)[:40])
+        try:
+            ep.forward(small[0], bias, small[1], small[2], *w, 2.5)
+            events.append("step2 ok")
+        except ValueError as exc:
+            events.append("step2 raised: " + str(exc)[:40])
+        torch.cuda.synchronize()
+        ret[rank] = events
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_batch_over_the_mapped_buffers_raises_on_every_rank_without_a_hang():
+    import torch.multiprocessing as mp
+    mgr = mp.get_context("spawn").Manager()
+    ret = mgr.dict()
+    mp.spawn(_overflow_worker, args=(2, _free_port(), ret), nprocs=2, join=True)
+    if ret[0] == ["no peer memory"]:
+        pytest.skip("symmetric memory unavailable: the NCCL form has no capacity")
+    assert ret[1][1].startswith("step1 raised") and ret[1][2].startswith("step2 raised"), ret[1]
+    assert ret[0][1] == "step1 ok" and ret[0][2].startswith("step2 raised"), ret[0]
