@@ -98,7 +98,9 @@ constexpr int kTmemCols = 2 * kBN;
 
 __device__ __forceinline__ float silu_mul(float g, float u) {
   float sig = __fdividef(1.0f, 1.0f + __expf(-u));   // approximate reciprocal: 2 ulp, far below e4m3 resolution
-  return g * (u * sig);
+  // The activations are stored as fp16: a product beyond its range saturates (the row then requantises to
+  // the largest e4m3 code) instead of becoming inf and, through an infinite row scale, NaN.
+  return fminf(fmaxf(g * (u * sig), -65504.0f), 65504.0f);
 }
 
 // acc[16 pairs] += scale * r[32] with packed fp32 FMAs (scalar FMAs measured the same)

@@ -52,7 +52,9 @@ template <int NT> struct DCfg {
 
 __device__ __forceinline__ float silu_mul_d(float g, float u) {
   float sig = __fdividef(1.0f, 1.0f + __expf(-u));
-  return g * (u * sig);
+  // The activations are stored as fp16: a product beyond its range saturates (the row then requantises to
+  // the largest e4m3 code) instead of becoming inf and, through an infinite row scale, NaN.
+  return fminf(fmaxf(g * (u * sig), -65504.0f), 65504.0f);
 }
 
 // 32 lanes x 16 consecutive fp32 columns
