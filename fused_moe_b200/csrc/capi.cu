@@ -259,7 +259,7 @@ int b200moe_launches_per_run(int T, int e_local) {
   const char* front = getenv("B200MOE_FRONT");
   const bool fused_front = T <= kFrontSmallMaxTokens && !(front && front[0] == '0');
   // route, scan, place, gather, gemm1, requant, gemm2 (+ weighted unpermute / reduce into the output); calls of at
-  // most 64 tokens fuse the first three, the decode GEMM1 (at most 16 tokens) also requantises
+  // most 32 tokens fuse the first three, the decode GEMM1 (at most 16 tokens) also requantises
   static const bool decode_on = [] {
     const char* v = getenv("B200MOE_DECODE");
     return !(v && v[0] == '0');

@@ -1,4 +1,4 @@
-// Routing, scan and placement of a decode-size call (at most 64 tokens) in ONE block.
+// Routing, scan and placement of a decode-size call (at most 32 tokens) in ONE block.
 //
 // At these sizes the three kernels it stands for (route.cu, and scan + place of permute.cu,
 // which replace the reference's `fused_route_topk_kernel`, `exclusive_scan_kernel` and
@@ -15,8 +15,7 @@ namespace b200moe {
 
 namespace {
 
-constexpr int kFrontWarps = 32;   // a warp routes tokens warp, warp + 32
-static_assert(kFrontSmallMaxTokens == 2 * kFrontWarps, "two tokens per warp, two lane rounds per expert");
+constexpr int kFrontWarps = kFrontSmallMaxTokens;   // one warp per token
 
 __global__ void __launch_bounds__(kFrontWarps * 32, 1)
 route_place_small_kernel(Workspace ws, const void* __restrict__ logits, int logits_dtype,
@@ -43,27 +42,23 @@ route_place_small_kernel(Workspace ws, const void* __restrict__ logits, int logi
   float* topk_w = ws.at<float>(ws.L.topk_w);
   int* tok_rows = ws.at<int>(ws.L.tok_rows);
 
-  // ---- route: warp w routes tokens w and w + 32
-  {
+  // ---- route: warp t routes token t
+  if (warp < T) {
     float b[kNumGroups];
 #pragma unroll
     for (int g = 0; g < kNumGroups; ++g) b[g] = load_as_float(bias, bias_dtype, g * 32 + lane);
-    for (int t = warp; t < kFrontSmallMaxTokens; t += kFrontWarps) {
-      if (t < T) {
-        int my_id;
-        float my_w;
-        route_one_token(logits, logits_dtype, t, b, rsf, lane, my_id, my_w);
-        if (lane < kTopK) {
-          topk_ids[(size_t)t * kTopK + lane] = my_id;
-          topk_w[(size_t)t * kTopK + lane] = my_w;
-          tok_rows[(size_t)t * kTopK + lane] = -1;   // local pairs are overwritten below
-          s_ids[lane][t] = my_id;
-          s_w[lane][t] = my_w;
-        }
-      } else if (lane < kTopK) {
-        s_ids[lane][t] = -1;
-      }
+    int my_id;
+    float my_w;
+    route_one_token(logits, logits_dtype, warp, b, rsf, lane, my_id, my_w);
+    if (lane < kTopK) {
+      topk_ids[(size_t)warp * kTopK + lane] = my_id;
+      topk_w[(size_t)warp * kTopK + lane] = my_w;
+      tok_rows[(size_t)warp * kTopK + lane] = -1;   // local pairs are overwritten below
+      s_ids[lane][warp] = my_id;
+      s_w[lane][warp] = my_w;
     }
+  } else if (lane < kTopK) {
+    s_ids[lane][warp] = -1;
   }
   if (threadIdx.x == 0) s_rows = 0;
   __syncthreads();
@@ -118,25 +113,20 @@ route_place_small_kernel(Workspace ws, const void* __restrict__ logits, int logi
     meta[3] = pad_rows;
   }
 
-  // ---- place: a warp walks an expert's tokens in token order (lane = token, two rounds of 32)
+  // ---- place: a warp walks an expert's tokens in token order (lane = token)
   for (int le = warp; le < e_local; le += kFrontWarps) {
     if (s_cnt[le] == 0) continue;
     const int want = le + local_off;
-    int pos = s_row0[le];
-    for (int t0 = 0; t0 < kFrontSmallMaxTokens; t0 += 32) {
-      const int t = t0 + lane;
-      int kf = -1;
+    int kf = -1;
 #pragma unroll
-      for (int k = 0; k < kTopK; ++k)
-        if (s_ids[k][t] == want) kf = k;
-      const uint32_t hit = __ballot_sync(0xffffffffu, kf >= 0);
-      if (kf >= 0) {
-        const int r = pos + __popc(hit & ((1u << lane) - 1u));
-        row_token[r] = t;
-        row_weight[r] = s_w[kf][t];
-        tok_rows[(size_t)t * kTopK + kf] = r;
-      }
-      pos += __popc(hit);
+    for (int k = 0; k < kTopK; ++k)
+      if (s_ids[k][lane] == want) kf = k;
+    const uint32_t hit = __ballot_sync(0xffffffffu, kf >= 0);
+    if (kf >= 0) {
+      const int r = s_row0[le] + __popc(hit & ((1u << lane) - 1u));
+      row_token[r] = lane;
+      row_weight[r] = s_w[kf][lane];
+      tok_rows[(size_t)lane * kTopK + kf] = r;
     }
   }
 }

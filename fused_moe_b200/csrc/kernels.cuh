@@ -44,7 +44,7 @@ cudaError_t launch_permute(const Workspace& ws, const int32_t* ids, long long id
 
 // Routing + scan + placement of at most kFrontSmallMaxTokens tokens in one block (front_small.cu);
 // writes the workspace's own topk_ids / topk_w.
-constexpr int kFrontSmallMaxTokens = 64;
+constexpr int kFrontSmallMaxTokens = 32;
 cudaError_t launch_route_place_small(const Workspace& ws, const void* logits, int logits_dtype, const void* bias,
                                      int bias_dtype, int T, float rsf, int local_off, int e_local, int pad_rows,
                                      cudaStream_t stream);
