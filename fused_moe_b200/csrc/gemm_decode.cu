@@ -90,7 +90,7 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
   const uint32_t bar_xready = bar_drain + 16;    // 2 barriers: u of an up warp is in shared memory
   const uint32_t bar_xfree = bar_xready + 16;    // 2 barriers: its gate warp has read it
   const uint32_t bar_split = bar_xfree + 16;     // 2 barriers (split K): partial sums written; arrival order known
-  const uint32_t bar_rq = bar_split + 16;        // 2 barriers (GEMM1): this item's activations stored; verdict known
+  const uint32_t bar_rq = bar_split + 16;        // 2 barriers (GEMM1): this item's activations stored; outcome of the arrival count known
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 2 * kRing + 10);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* split_flag = reinterpret_cast<volatile int*>(tmem_slot + 3);
