@@ -205,7 +205,10 @@ cudaError_t launch_permute(const Workspace& ws, const int32_t* ids, long long id
                            local_off, e_local, n_rows_dev);
       if (err != cudaSuccess) return err;
     }
-    long long cap_rows = ws.L.m_cap;
+    // padded rows of this call: at most 8 T pairs plus 127 rows of padding per expert that has any
+    const long long pairs = (long long)T * kTopK;
+    long long cap_rows = pairs + (long long)(kTileM - 1) * (pairs < e_local ? pairs : e_local);
+    if (cap_rows > ws.L.m_cap) cap_rows = ws.L.m_cap;
     int blocks = (int)((cap_rows + 7) / 8);
     int cap = num_sms * 8;
     if (blocks > cap) blocks = cap;
