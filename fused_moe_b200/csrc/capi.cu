@@ -127,6 +127,8 @@ int make_tmap_gate_up(CUtensorMap* map, const void* base, uint64_t e_local, uint
 
 uint64_t align_up(uint64_t x, uint64_t a) { return (x + a - 1) / a * a; }
 
+constexpr int kDirectRowsMaxTokens = 8;   // largest call whose decode GEMM1 reads the caller's rows in place
+
 // Decode-size calls (up to 16 tokens) take the swapped-operand kernels (B200MOE_DECODE=0 turns them off;
 // B200MOE_DECODE=64 extends them to 64 tokens, where the 128-row tiles currently measure faster).  Their
 // per-warp scale panels hold a bounded number of K blocks; larger shapes take the grouped kernels.
@@ -269,7 +271,9 @@ int b200moe_launches_per_run(int T, int e_local) {
     return (v && v[0] == '6') ? 64 : 16;
   }();
   const int requant = (decode_on && T <= decode_max_t) ? 0 : 1;   // decode GEMM1 requantises by itself
-  return (fused_front ? 4 : 6) + requant;
+  // ... and, behind the fused front kernel, fetches the token rows itself: no gather pass (three launches)
+  const int gather = (fused_front && decode_on && T <= kDirectRowsMaxTokens) ? 0 : 1;
+  return (fused_front ? 3 : 5) + gather + requant;
 }
 
 int b200moe_route(const void* logits, int logits_dtype, const void* bias, int bias_dtype, int T,
@@ -343,18 +347,28 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
   if ((rc = ensure_device(&num_sms)) != B200MOE_OK) return rc;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 
-  // (the gather kernel also zeroes the output rows, which GEMM2's epilogue adds into)
-  CUDA_TRY(launch_permute(ws, topk_ids, ids_row_stride, topk_w, w_row_stride, hidden_states, hidden_row_stride,
-                          hidden_scale, scale_stride_t, scale_stride_kb, T, e_local, local_expert_offset, hidden,
-                          kTileM, num_sms, st, placed, segs, out_bf16, out_row_stride, segs_dev, n_rows_dev));
-
   const int nt = decode_tile(T, hidden, inter);
+  // A call of at most 8 tokens that the one-block front kernel routed and placed runs no gather pass: its GEMM1
+  // fetches the token rows and their scales where the caller keeps them (and zeroes the output rows).  Measured
+  // with inputs cold in HBM: -4 us at 1 token, -2 at 4, but +2..4 at 16 tokens with 4 rows (56 separate 128-byte
+  // pieces per row instead of one coalesced pass), hence the limit.
+  const bool direct_a = placed && nt == 16 && T <= kDirectRowsMaxTokens && !segs && !segs_dev;
+  // (the gather kernel also zeroes the output rows, which GEMM2's epilogue adds into)
+  if (!direct_a)
+    CUDA_TRY(launch_permute(ws, topk_ids, ids_row_stride, topk_w, w_row_stride, hidden_states, hidden_row_stride,
+                            hidden_scale, scale_stride_t, scale_stride_kb, T, e_local, local_expert_offset, hidden,
+                            kTileM, num_sms, st, placed, segs, out_bf16, out_row_stride, segs_dev, n_rows_dev));
 
   GemmParams g1;
   memset(&g1, 0, sizeof(g1));
-  if ((rc = make_tmap(&g1.tmap_a, ws.base + ws.L.a_packed, (uint64_t)ws.L.m_cap, (uint64_t)hidden, (uint64_t)hidden,
-                      nt ? nt : kTileM)) != B200MOE_OK)
+  if (direct_a) {   // the caller's rows, one row per box
+    if ((rc = make_tmap(&g1.tmap_a, hidden_states, (uint64_t)T, (uint64_t)hidden, (uint64_t)hidden_row_stride, 1)) !=
+        B200MOE_OK)
+      return rc;
+  } else if ((rc = make_tmap(&g1.tmap_a, ws.base + ws.L.a_packed, (uint64_t)ws.L.m_cap, (uint64_t)hidden,
+                             (uint64_t)hidden, nt ? nt : kTileM)) != B200MOE_OK) {
     return rc;
+  }
   // one box = 128 gate rows + the matching 128 up rows (decode kernels: 64 + 64)
   if ((rc = make_tmap_gate_up(&g1.tmap_b, w1, (uint64_t)e_local, (uint64_t)inter, (uint64_t)hidden, nt ? 64 : 128)) !=
       B200MOE_OK)
@@ -376,6 +390,13 @@ static int experts_impl(const int32_t* topk_ids, int64_t ids_row_stride, const f
   g1.tile_done = ws.at<int>(ws.L.tile_done);
   g1.act_q_out = ws.at<uint8_t>(ws.L.act_q);
   g1.row_scale_out = ws.at<float>(ws.L.row_scale);
+  g1.direct_a = direct_a ? 1 : 0;
+  g1.zero_tokens = direct_a ? T : 0;   // no gather pass: GEMM1's CTAs zero the output rows that GEMM2 adds into
+  g1.out = reinterpret_cast<__nv_bfloat16*>(out_bf16);
+  g1.out_stride = out_row_stride;
+  g1.hscale = hidden_scale;
+  g1.hs_stride_t = scale_stride_t;
+  g1.hs_stride_kb = scale_stride_kb;
   g1.status = ws.at<int>(ws.L.status);
   g1.status_mirror = g_status_mirror;
   g1.splitk_scratch = ws.at<float>(ws.L.splitk_scratch);

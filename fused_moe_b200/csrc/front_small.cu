@@ -41,6 +41,7 @@ route_place_small_kernel(Workspace ws, const void* __restrict__ logits, int logi
   int32_t* topk_ids = ws.at<int32_t>(ws.L.topk_ids);
   float* topk_w = ws.at<float>(ws.L.topk_w);
   int* tok_rows = ws.at<int>(ws.L.tok_rows);
+  unsigned* row_amax = ws.at<unsigned>(ws.L.row_amax);
 
   // ---- route: warp t routes token t
   if (warp < T) {
@@ -126,6 +127,7 @@ route_place_small_kernel(Workspace ws, const void* __restrict__ logits, int logi
       const int r = s_row0[le] + __popc(hit & ((1u << lane) - 1u));
       row_token[r] = lane;
       row_weight[r] = s_w[kf][lane];
+      row_amax[r] = 0u;   // GEMM1's epilogue takes the running maximum with atomicMax
       tok_rows[(size_t)lane * kTopK + kf] = r;
     }
   }

@@ -137,6 +137,15 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
   // kernels is read from here on.
   chain_wait();
   chain_release();
+  if (MODE == 1 && p.zero_tokens > 0) {
+    // no gather pass ran: the output rows that GEMM2 adds into are zeroed here, a few stores per CTA
+    const int vec_per_row = p.hidden / 8;   // 8 bf16 = 16 bytes
+    const long long total = (long long)p.zero_tokens * vec_per_row;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+      const long long t = i / vec_per_row;
+      reinterpret_cast<uint4*>(p.out + t * p.out_stride)[i - t * vec_per_row] = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
   const int m_tiles = p.meta[0];
   const int tiles = m_tiles * p.n_tiles;
   const int kblocks = p.kblocks;
@@ -168,6 +177,18 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
         // GEMM1: 64 gate rows + the matching 64 up rows of expert e, one 3D box over its two planes;
         // GEMM2: 128 consecutive rows of [e_local*hidden][inter]
         const int wrow = MODE == 1 ? slab * 64 : e * p.n_per_expert + slab * kSlabRows;
+        // Without a gather pass (GEMM1 of a call that was routed and placed by the one-block front kernel) the
+        // expert's token rows are fetched where the caller keeps them: one one-row box per row and K block (an
+        // expert has one or two rows at these sizes); rows past the expert's count keep whatever the stage held,
+        // as padding rows do, and their columns are never stored.
+        const bool direct = MODE == 1 && NT == 16 && p.direct_a != 0;
+        int cnt = 0;
+        int toks[16];
+        if (direct) {
+          cnt = min(p.expert_count[e], 16);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) toks[j] = j < cnt ? p.row_token[m_tile * kTileM + j] : 0;
+        }
         for (int kb = ks * kbs; kb < (ks + 1) * kbs; ++kb, ++it) {
           if ((it % kProducers) != pme) continue;
           const uint32_t s = it % S, ph = (it / S) & 1u;
@@ -176,10 +197,16 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
           const long long q1 = PROF ? clock64() : 0;
           const uint32_t full = bar_full + 8 * s;
           const uint32_t w_dst = smem_base + s * Cfg::kStageBytes;
-          mbar_arrive_expect_tx(full, Cfg::kStageBytes);
+          mbar_arrive_expect_tx(full, direct ? kWBytes + cnt * kBlockK : Cfg::kStageBytes);
           if (MODE == 1) tma_load_3d(w_dst, &p.tmap_b, kb * kBlockK, wrow, 2 * e, full);
           else tma_load_2d(w_dst, &p.tmap_b, kb * kBlockK, wrow, full);
-          tma_load_2d(w_dst + kWBytes, &p.tmap_a, kb * kBlockK, m_tile * kTileM, full);
+          if (direct) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (j < cnt) tma_load_2d(w_dst + kWBytes + j * kBlockK, &p.tmap_a, kb * kBlockK, toks[j], full);
+          } else {
+            tma_load_2d(w_dst + kWBytes, &p.tmap_a, kb * kBlockK, m_tile * kTileM, full);
+          }
           if (PROF) { pw += q1 - q0; pi += clock64() - q1; }
         }
       }
@@ -258,7 +285,16 @@ decode_gemm_kernel(const __grid_constant__ GemmParams p) {
       float* panel_sb = panel + Cfg::kMaxKBlocks * NT;     // this warp's weight scales, one per K block
       __syncwarp();
       for (int i = lane; i < kblocks; i += 32) panel_sb[i] = sb_ptr[i];
-      if (MODE == 1) {
+      if (MODE == 1 && NT == 16 && p.direct_a) {
+        // the token scales where the caller keeps them: lane j < 16 knows row j's token
+        const int n_rows = min(p.expert_count[e], NT);
+        const int my_tok = lane < n_rows ? p.row_token[row0 + lane] : -1;
+        const int tj = __shfl_sync(0xffffffffu, my_tok, lane & (NT - 1));   // entry i belongs to row i % 16 = lane % 16
+        for (int i = lane; i < kblocks * NT; i += 32) {
+          const int kb = i / NT;
+          panel[i] = tj >= 0 ? p.hscale[(size_t)tj * p.hs_stride_t + (size_t)kb * p.hs_stride_kb] : 0.f;
+        }
+      } else if (MODE == 1) {
         for (int i = lane; i < kblocks * (NT / 4); i += 32) {
           const int kb = i / (NT / 4), v = i % (NT / 4);
           reinterpret_cast<float4*>(panel)[i] = reinterpret_cast<const float4*>(sa_ptr + (size_t)kb * p.m_cap)[v];

@@ -80,6 +80,12 @@ struct GemmParams {
   const float* row_weight;  // GEMM2 in: routing weight per row
   __nv_bfloat16* out;       // GEMM2 out: the layer's output rows [T][out_stride], zeroed at call start; every packed
   long long out_stride;     //            row is added into its token's row (bf16 red.global.add)
+  // decode GEMM1 without a gather pass: tmap_a covers the caller's hidden states [T][K] with one-row boxes, a row's
+  // 1x128 scales are read at hscale[token * hs_stride_t + kb * hs_stride_kb]
+  int direct_a;
+  int zero_tokens;          // ... and this many rows of `out` are zeroed by GEMM1's CTAs (GEMM2 adds into them)
+  const float* hscale;
+  long long hs_stride_t, hs_stride_kb;
   int* status;
   int* status_mirror;       // optional host-mapped int32[4]: receives the status word when a CTA gives up on a wait
   float* splitk_scratch;    // decode GEMMs: [kSplitKSlots][kSplitKMax][16][128] partial sums

@@ -4,6 +4,8 @@ Reads the intermediates out of the workspace (layout from ``b200moe_workspace_la
 checks each against the oracle's value for that stage, so a failure names the first kernel
 that went wrong instead of only the final output.
 """
+import os
+
 import numpy as np
 import torch
 
@@ -64,6 +66,10 @@ def check_stages(inp_cpu, res, ws, act_rtol=2e-3, verbose=False):
     amax_bits = ws.view("row_amax", torch.int32, (L.m_cap,))[:m_pad].cpu().numpy()
     act_q = ws.view("act_q", torch.uint8, (L.m_cap, inter))[:m_pad].cpu().numpy()
     row_scale = ws.view("row_scale", torch.float32, (L.m_cap,))[:m_pad].cpu().numpy()
+    # a call of at most 8 tokens through the fused front kernel runs no gather pass (its GEMM1 reads the caller's rows in place;
+    # the activations checked below prove that it read the right rows and scales)
+    gathered = not (T <= 8 and os.environ.get("B200MOE_FRONT", "1") != "0"
+                    and os.environ.get("B200MOE_DECODE", "1") != "0")
     hs = inp_cpu.hidden_states.view(torch.uint8).numpy()
     hsc = O.hidden_scale_rows(inp_cpu.hidden_states_scale.numpy(), T, hidden // 128)
     worst_act = 0.0
@@ -77,8 +83,9 @@ def check_stages(inp_cpu, res, ws, act_rtol=2e-3, verbose=False):
         st = ora["stages"][e]
         assert np.array_equal(row_token[r0:r0 + n], st["rows"]), f"permute: token order of expert {e}"
         np.testing.assert_array_equal(row_weight[r0:r0 + n], st["w"], err_msg=f"permute: weights of expert {e}")
-        assert np.array_equal(a_packed[r0:r0 + n], hs[st["rows"]]), f"gather: payload of expert {e}"
-        assert np.array_equal(a_scale[:, r0:r0 + n].T, hsc[st["rows"]]), f"gather: scales of expert {e}"
+        if gathered:
+            assert np.array_equal(a_packed[r0:r0 + n], hs[st["rows"]]), f"gather: payload of expert {e}"
+            assert np.array_equal(a_scale[:, r0:r0 + n].T, hsc[st["rows"]]), f"gather: scales of expert {e}"
         # --- GEMM1 + SwiGLU
         ref_act = st["act"]
         scale_ref = np.abs(ref_act).max() + 1e-6
