@@ -48,7 +48,7 @@ UNIT = "tokens/s"
 
 # DRAM traffic of one GEMM1 launch per packed row and per active expert, from the ncu
 # capture summarised under profiles/ (None until a capture exists).
-NCU_TRAFFIC = {"per_row": 14858.0, "per_expert": 31.04e6}   # profiles/grouped_gemm_slice8192_zipf2048.md
+NCU_TRAFFIC = {"per_row": 14812.0, "per_expert": 31.02e6}   # profiles/grouped_gemm_slice8192_zipf2048.md
 
 
 def bind_to_gpu_numa_node(local_rank: int):
