@@ -83,6 +83,19 @@ def test_entry_points_reject_bad_arguments_before_touching_cuda():
     assert lib.b200moe_ep_pack(p, p, p, 512, p, 1, 1, 8, 512, 3, p, p, p, None) == -2
     assert lib.b200moe_ep_pack(p, p, p, 512, p, 1, 1, 8, 256, 2, p, p, p, None) == -2
     assert lib.b200moe_ep_combine(p, p, p, 8, 512, 5, p, None) == -2
+    # the peer-memory step: world size, row pitch and null buffers are checked before any CUDA call
+    bases = (C.c_void_p * 2)(p, p)
+    args = (bases, p, 2, 64, 7168 + 224 + 64, p, p, p, p, 32, 0, 7168, 2048, base, L.total_bytes, p, 7168, None)
+    assert lib.b200moe_ep_local_experts(*args[:2], 3, *args[3:]) == -2
+    assert lib.b200moe_ep_local_experts(*args[:4], 7168 + 224 + 60, *args[5:]) == -6
+    assert lib.b200moe_ep_local_experts(None, *args[1:]) == -1
+
+
+def test_launch_counts_per_call():
+    """Kernels per layer call with the default switches: seven; calls of at most 32 tokens fuse routing, scan and
+    placement; the decode GEMM1 (at most 16 tokens) also requantises; at most 8 tokens need no gather pass."""
+    lib = _capi.lib()
+    assert [lib.b200moe_launches_per_run(T, 32) for T in (0, 1, 8, 9, 16, 17, 32, 33, 4096)] == [0, 3, 3, 4, 4, 5, 5, 7, 7]
 
 
 def test_host_entry_point_refuses_cpu_tensors_and_bad_shapes():
