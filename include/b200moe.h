@@ -145,8 +145,10 @@ B200MOE_API int b200moe_count(const int32_t* topk_ids, int64_t ids_row_stride, i
                   int local_expert_offset, int e_local, int hidden, int inter,
                   void* workspace, size_t workspace_bytes, void* stream);
 
-/* Expert MLPs + combine for given routing; the counters in the workspace must have been
- * filled by b200moe_route or b200moe_count for the same ids on the same stream.
+/* Expert MLPs + routing-weighted reduce for given routing; the counters in the workspace must have been
+ * filled by b200moe_route or b200moe_count for the same ids on the same stream.  The call zeroes the T
+ * output rows itself and GEMM2's epilogue adds every (token, expert) row into its token's row in bf16
+ * (no combine pass; the sum order follows tile completion, so two runs agree to a few bf16 steps).
  * Replaces `fused_dispatch`, `fused_gather_hidden_scales`, `moe_blockwise_grouped_mm_v2`
  * (x2), `swiglu_fp8_requant*`, `weighted_scatter` / `reduce_scatter_unweighted_fused`
  * (moe_fused.cu:131-542, 736-1150; moe_gemm.cu:527-654).
